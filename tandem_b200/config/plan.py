@@ -50,10 +50,14 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class NormSpec(PartSpec):
+    """kind "rmsnorm": the row divided by its root mean square, times a weight.  kind "group_rmsnorm": the row in
+    ``groups`` equal consecutive runs, each divided by its own root mean square, the whole times the weight."""
+
     family = "norm"
     size: int = 0
     eps: float = 1e-6
     weight: str = ""  # checkpoint tensor name
+    groups: int = 1
 
 
 @dataclass(frozen=True)
@@ -186,14 +190,52 @@ class SelectiveRecurrenceSpec(MixerSpec):
 
 
 @dataclass(frozen=True)
+class RotaryScalingSpec:
+    """Frequencies stretched for sequences longer than ``original`` tokens, pair by pair.  With n(t) =
+    dims ln(original / (2 pi t)) / (2 ln base) the pair index whose wave makes t turns in ``original`` tokens,
+    lo = max(floor(n(fast)), 0) and hi = min(ceil(n(slow)), dims - 1): pair i keeps the share 1 - ramp_i of its
+    frequency and takes the share ramp_i of frequency / ``factor``, ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1);
+    cos and sin are multiplied by 0.1 ln(factor) + 1."""
+
+    factor: float
+    original: float
+    fast: float
+    slow: float
+
+
+def rotary_table(dims: int, base: float, scaling: Optional["RotaryScalingSpec"] = None) -> tuple:
+    """(frequency of every pair, factor on cos and sin) in double precision for a rotation of ``dims`` numbers."""
+    import math
+
+    freq = [float(base) ** (-2.0 * i / dims) for i in range(dims // 2)]
+    if scaling is None:
+        return freq, 1.0
+
+    def pair_of(turns: float) -> float:
+        return dims * math.log(scaling.original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(pair_of(scaling.fast)), 0)
+    hi = min(math.ceil(pair_of(scaling.slow)), dims - 1)
+    out = []
+    for i, f in enumerate(freq):
+        ramp = min(1.0, max(0.0, (i - lo) / max(hi - lo, 0.001)))
+        out.append(f / scaling.factor * ramp + f * (1.0 - ramp))
+    return out, 0.1 * math.log(scaling.factor) + 1.0
+
+
+@dataclass(frozen=True)
 class LatentAttentionSpec(MixerSpec):
     """Causal softmax attention whose keys and values are expanded from a latent of ``latent_dim``
     numbers per token (RMS-normed with a weight), plus one rotated key part of ``rotary_dim``
     numbers that all heads share; a query head is [``head_dim`` unrotated | ``rotary_dim`` rotated].
-    The rotation (rotate_half pairing, angle = position * base^(-2 i / rotated_dims)) turns the first
-    ``rotated_dims`` numbers of the rotated part.
-    Only the latent and the rotated key part are cached.  ``gate``: "sigmoid" multiplies the
-    concatenated heads by sigmoid of a projection of the mixer's input, "none" leaves them.
+    The rotation (angle = position * base^(-2 i / rotated_dims), frequencies stretched where
+    ``rotary_scaling`` says so) turns the first ``rotated_dims`` numbers of the rotated part, paired
+    (i, i + rotated_dims / 2) (``rotary_pairing`` "half") or (2 i, 2 i + 1) ("interleaved").
+    Only the latent and the rotated key part are cached.  ``query_latent_dim`` > 0: the queries come
+    through a latent of their own, q = W_uq RMSNorm(W_dq x) (tensors ``.dq``, ``.dq.norm``, ``.uq``
+    instead of ``.q``).  ``gate``: "sigmoid" multiplies the concatenated heads by sigmoid of a
+    projection of the mixer's input (``.g`` [heads * value_dim, hidden]), "sigmoid_head" each head by one
+    such number (``.g`` [heads, hidden]), "none" leaves them.
     Checkpoint tensors ``<prefix>.q``, ``.dkv``, ``.dkv.norm``, ``.uk``, ``.uv``, ``.g``, ``.o``."""
 
     hidden_size: int = 0
@@ -208,6 +250,21 @@ class LatentAttentionSpec(MixerSpec):
     norm_eps: float = 1e-6
     gate: str = "sigmoid"
     names: tuple = ()
+    rotary_pairing: str = "half"
+    rotary_scaling: Optional[RotaryScalingSpec] = None
+    query_latent_dim: int = 0
+
+
+@dataclass(frozen=True)
+class ShortConvolutionSpec(MixerSpec):
+    """A causal convolution over time on every channel of the stream, in front of a sublayer:
+    h_t = x_t + sum_j w[c, j] x_(t - taps + 1 + j) (``skip`` False: without x_t), zeros in front of a
+    sequence.  A request's last ``taps`` - 1 inputs are its state.  Checkpoint tensor ``weight`` [hidden, taps]."""
+
+    hidden_size: int = 0
+    taps: int = 1
+    weight: str = ""
+    skip: bool = True
 
 
 @dataclass(frozen=True)
@@ -231,7 +288,11 @@ class RoutedMLPSpec(FeedForwardSpec):
     ``top_k``: router logits W_router x in float32, scores by ``score`` ("sigmoid" | "softmax"), the
     ``top_k`` largest scores chosen, their scores divided by their sum (+ 1e-20) where ``normalize``,
     times ``route_scale``; the output is the weighted sum of the chosen experts' outputs.  Checkpoint
-    tensors ``<prefix>.router`` [experts, hidden], ``<prefix>.e<i>.gate``, ``.up``, ``.down``."""
+    tensors ``<prefix>.router`` [experts, hidden], ``<prefix>.e<i>.gate``, ``.up``, ``.down``.
+    ``gated`` False: an expert is down(act(up x)) (no ``.gate`` tensors; ``activation`` "gelu", the exact
+    one).  ``identity_experts`` n: the router has n outputs more, behind the experts'; a token that
+    chooses one of them gets its own input back for it (times the weight).  ``choice_bias``: a tensor
+    ``<prefix>.<choice_bias>`` [router outputs] is added to the scores for the choice only."""
 
     hidden_size: int = 0
     intermediate_size: int = 0  # of one expert
@@ -241,6 +302,9 @@ class RoutedMLPSpec(FeedForwardSpec):
     normalize: bool = True
     route_scale: float = 1.0
     activation: str = "silu"
+    gated: bool = True
+    identity_experts: int = 0
+    choice_bias: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -271,6 +335,18 @@ class StreamLinkSpec(ConnectionSpec):
     streams: int = 1
     mult: float = 1.0
     prefix: Optional[str] = None
+
+
+@dataclass(frozen=True)
+class DepthAverageSpec(ConnectionSpec):
+    """What a layer hands on is a learned weighted sum of the results of all layers so far:
+    x <- sum_(j <= n) a[j] Y_j with Y_0 the start of the stream and Y_n this layer's own result (``count`` =
+    n + 1 coefficients in the checkpoint tensor ``weight``).  The layer with two coefficients is the first: what it
+    receives is Y_0.  ``total``: how many results the model makes in all, Y_0 included (the room kept for them)."""
+
+    count: int = 1
+    weight: str = ""
+    total: int = 1
 
 
 @dataclass(frozen=True)
@@ -329,6 +405,7 @@ class EmbeddingSpec:
     scale: float = 1.0
     positions: Optional[str] = None
     copies: int = 1  # the residual starts as so many equal streams side by side, [T, copies * hidden]
+    norm: Optional[NormSpec] = None  # applied to the embedded rows before the first layer
 
 
 @dataclass(frozen=True)

@@ -47,6 +47,7 @@ struct WideArgs {
   int* status;
   int M, N, K;       // N: rows of W; with `gated`, N = 2 I
   int out_f32, gated;
+  int act;  // on the bfloat16 output without a gate: 0 none, 1 the exact GELU
   int m_tiles, n_tiles;
   int wn;  // rows of W per tile: a multiple of 32 from 128 to 256 (with `gated`: half of them gate rows, half up rows)
   // Grouped products (routed experts): W holds one [N, K] matrix per group, one behind the other, and every tile of
@@ -238,6 +239,10 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 if (n0 + c < a.N) *reinterpret_cast<float4*>(dst + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);  // N is a multiple of 8
             } else {
               __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.y) + (size_t)row * a.N + n0;
+              if (a.act == 1) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) v[c] = 0.5f * v[c] * (1.f + erff(v[c] * 0.70710678118654752f));
+              }
 #pragma unroll
               for (int c = 0; c < 32; c += 8)
                 if (n0 + c < a.N)
@@ -299,9 +304,11 @@ extern "C" {
 // I a multiple of 8): y [M, I] = silu(x w[:I]^T) * (x w[I:]^T).  K and N multiples of 8.
 // Grouped: w holds `groups` matrices [N, K] one behind the other, x [M, K] has M a multiple of 128 and every 128 rows of
 // it belong to the group tile_group[tile] (int32 on the device; -1: no rows there, nothing is computed or written).
-int tb_gemm_wide_grouped(void* stream, const void* x, const void* w, void* y, int* status, int M, int N, int K, int out_f32,
-                         int gated, int blocks, const int* tile_group, int groups) {
+// act (bfloat16 output without a gate): 0 none, 1 the exact GELU on every output.
+int tb_gemm_wide_grouped_act(void* stream, const void* x, const void* w, void* y, int* status, int M, int N, int K, int out_f32,
+                             int gated, int blocks, const int* tile_group, int groups, int act) {
   if (M <= 0 || N <= 0) return 0;
+  if (act < 0 || act > 1 || (act && (gated || out_f32))) return TB_ERR_BAD_SIZE;
   if (K <= 0 || K % 8 != 0 || N % 8 != 0 || blocks <= 0 || groups <= 0 || (tile_group && M % tb::WM != 0) || (!tile_group && groups != 1))
     return TB_ERR_BAD_SIZE;
   if (gated && (out_f32 || N % 16 != 0)) return TB_ERR_BAD_SIZE;
@@ -331,6 +338,7 @@ int tb_gemm_wide_grouped(void* stream, const void* x, const void* w, void* y, in
   tb::WideArgs a;
   a.y = y; a.status = status; a.M = M; a.N = N; a.K = K; a.out_f32 = out_f32; a.gated = gated;
   a.wn = wn;
+  a.act = act;
   a.tile_group = tile_group;
   a.m_tiles = m_tiles;
   a.n_tiles = gated ? (N / 2 + wn / 2 - 1) / (wn / 2) : (N + wn - 1) / wn;
@@ -338,9 +346,14 @@ int tb_gemm_wide_grouped(void* stream, const void* x, const void* w, void* y, in
   return tb::launch(tb::gemm_wide_kernel, dim3(tiles < blocks ? tiles : blocks), dim3(tb::W_THREADS), smem, stream, map_x, map_w, a);
 }
 
+int tb_gemm_wide_grouped(void* stream, const void* x, const void* w, void* y, int* status, int M, int N, int K, int out_f32,
+                         int gated, int blocks, const int* tile_group, int groups) {
+  return tb_gemm_wide_grouped_act(stream, x, w, y, status, M, N, K, out_f32, gated, blocks, tile_group, groups, 0);
+}
+
 int tb_gemm_wide(void* stream, const void* x, const void* w, void* y, int* status, int M, int N, int K, int out_f32,
                  int gated, int blocks) {
-  return tb_gemm_wide_grouped(stream, x, w, y, status, M, N, K, out_f32, gated, blocks, nullptr, 1);
+  return tb_gemm_wide_grouped_act(stream, x, w, y, status, M, N, K, out_f32, gated, blocks, nullptr, 1, 0);
 }
 
 }  // extern "C"

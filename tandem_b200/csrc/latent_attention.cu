@@ -12,47 +12,51 @@
 // rotates the rotated part of every query head in place; `head_linear` is the small product per head
 // that folds W_uk into the queries in front of the attention kernel and applies W_uv behind it.
 // The attention itself is the package's kernel for keys and values of different sizes.
-// Rotation: rotate_half pairing (i, i + rd/2) of the first rd numbers of the rotated part, angle =
-// position * freq[i] in float32.  All arithmetic float32; T is the storage type of the cache.
+// Rotation of the first rd numbers of the rotated part: pairs (i, i + rd/2), or (2 i, 2 i + 1) where the model
+// interleaves them; angle = position * freq[pair] in float32 (the caller's table: any scaling of the frequencies is
+// already in it), cos and sin times one factor.  All arithmetic float32; T is the storage type of the cache.
 #include "cache_layout.cuh"
 #include "common.cuh"
 
 namespace tb {
 
-// One block per token.  proj float32 [T, stride]: H query heads of (d + r) numbers from column 0, the
-// down-projection (R + r numbers) from column kv_col.  q_out float32 [T, H, R + r]: the rotated query part
-// is written to columns R .. R + r of each head (the first R columns are filled by head_linear).
+// Number i of a rotated part (r numbers of which the first rd are turned) at position pos.  Pairing: (i, i + rd / 2),
+// or with `interleaved` (2 i, 2 i + 1); pair n turns by the angle pos * freq[n]; cos and sin carry the factor `mag`.
+__device__ __forceinline__ float turned(const float* __restrict__ src, int i, int rd, int interleaved, float pos,
+                                        const float* __restrict__ freq, float mag) {
+  if (i >= rd) return src[i];
+  const int half = rd >> 1;
+  const bool first = interleaved ? !(i & 1) : i < half;
+  const int pair = interleaved ? i >> 1 : (first ? i : i - half);
+  const int other = interleaved ? i ^ 1 : (first ? i + half : i - half);
+  const float a = pos * freq[pair];
+  const float cs = cosf(a) * mag, sn = sinf(a) * mag;
+  return first ? src[i] * cs - src[other] * sn : src[i] * cs + src[other] * sn;
+}
+
+// One block per token.  q_in float32 rows of H query heads of (d + r) numbers; kv_in float32 rows of the
+// down-projection (R + r numbers).  q_out float32 [T, H, R + r]: the rotated query part is written to columns
+// R .. R + r of each head (the first R columns are filled by head_linear).
 template <typename T>
-__global__ void latent_prep_kernel(const float* __restrict__ proj, int stride, int kv_col, const float* __restrict__ norm_w,
+__global__ void latent_prep_kernel(const float* __restrict__ q_in, long long q_stride, const float* __restrict__ kv_in,
+                                   long long kv_stride, const float* __restrict__ norm_w,
                                    const float* __restrict__ freq, const int* __restrict__ positions,
                                    const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                    float* __restrict__ q_out, int H, int d, int r, int rd, int R, int page_size, float eps,
-                                   int write_kv) {
+                                   int write_kv, int interleaved, float mag) {
   __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
-  const float* row = proj + (size_t)t * stride;
+  const float* row = q_in + (size_t)t * q_stride;
   const float pos = (float)positions[t];
-  const int half = rd >> 1;
   // the rotated part of every query head
   for (int e = threadIdx.x; e < H * r; e += blockDim.x) {
     const int h = e / r, i = e % r;
-    const float* src = row + (size_t)h * (d + r) + d;
-    float v;
-    if (i < half) {
-      const float a = pos * freq[i];
-      v = src[i] * cosf(a) - src[i + half] * sinf(a);
-    } else if (i < rd) {
-      const float a = pos * freq[i - half];
-      v = src[i] * cosf(a) + src[i - half] * sinf(a);
-    } else {
-      v = src[i];
-    }
-    q_out[((size_t)t * H + h) * (R + r) + R + i] = v;
+    q_out[((size_t)t * H + h) * (R + r) + R + i] = turned(row + (size_t)h * (d + r) + d, i, rd, interleaved, pos, freq, mag);
   }
   // the cache entry
-  const float* kv = row + kv_col;
+  const float* kv = kv_in + (size_t)t * kv_stride;
   float ss = 0.f;
   for (int i = threadIdx.x; i < R; i += blockDim.x) ss = fmaf(kv[i], kv[i], ss);
   ss = block_sum(ss, scratch);
@@ -68,20 +72,8 @@ __global__ void latent_prep_kernel(const float* __restrict__ proj, int stride, i
     ktile[cache_offset<T>(rr, i, page_size, dk)] = c;
     vtile[cache_offset<T>(rr, i, page_size, R)] = c;
   }
-  for (int i = threadIdx.x; i < r; i += blockDim.x) {
-    const float* src = kv + R;
-    float v;
-    if (i < half) {
-      const float a = pos * freq[i];
-      v = src[i] * cosf(a) - src[i + half] * sinf(a);
-    } else if (i < rd) {
-      const float a = pos * freq[i - half];
-      v = src[i] * cosf(a) + src[i - half] * sinf(a);
-    } else {
-      v = src[i];
-    }
-    ktile[cache_offset<T>(rr, R + i, page_size, dk)] = from_float<T>(v);
-  }
+  for (int i = threadIdx.x; i < r; i += blockDim.x)
+    ktile[cache_offset<T>(rr, R + i, page_size, dk)] = from_float<T>(turned(kv + R, i, rd, interleaved, pos, freq, mag));
 }
 
 // out[t, h, n] = sum_k x[t, h, k] * W[h][n, k]  (or W[h][k, n] with `transposed`).  A block serves one head and
@@ -129,16 +121,17 @@ head_linear_kernel(const X* __restrict__ x, long long x_stride, int x_head, cons
   }
 }
 
-// y[t, c] = o[t, c] * sigmoid(g[t, c]), rounded to T.  o of type T, g float32 rows with stride g_stride.
+// y[t, c] = o[t, c] * sigmoid(g[t, c / per]), rounded to T.  o float32, g float32 rows with stride g_stride (per = 1: a gate
+// value per output; per = the value size of a head: one per head).
 template <typename T>
 __global__ void sigmoid_gate_kernel(const float* __restrict__ o, const float* __restrict__ g, int g_stride, T* __restrict__ y,
-                                    long long total, int N) {
+                                    long long total, int N, int per) {
   pdl_launch_dependents();
   pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const long long t = i / N;
     const int c = (int)(i % N);
-    const float gate = g ? 1.f / (1.f + expf(-g[(size_t)t * g_stride + c])) : 1.f;
+    const float gate = g ? 1.f / (1.f + expf(-g[(size_t)t * g_stride + c / per])) : 1.f;
     y[i] = from_float<T>(o[i] * gate);
   }
 }
@@ -147,14 +140,17 @@ __global__ void sigmoid_gate_kernel(const float* __restrict__ o, const float* __
 
 extern "C" {
 
-int tb_latent_prep(void* stream, const float* proj, int stride, int kv_col, const float* norm_w, const float* freq,
-                   const int* positions, const int* slots, void* k_cache, void* v_cache, float* q_out, int T_tokens, int H, int d,
-                   int r, int rd, int R, int page_size, float eps, int write_kv, int dtype) {
+// q_in: rows of H heads of d + r numbers (row stride q_stride floats); kv_in: rows of R + r numbers (row stride kv_stride).
+// interleaved: pairs (2 i, 2 i + 1) instead of (i, i + rd / 2); mag: factor on cos and sin.
+int tb_latent_prep(void* stream, const float* q_in, long long q_stride, const float* kv_in, long long kv_stride, const float* norm_w,
+                   const float* freq, const int* positions, const int* slots, void* k_cache, void* v_cache, float* q_out,
+                   int T_tokens, int H, int d, int r, int rd, int R, int page_size, float eps, int write_kv, int interleaved, float mag,
+                   int dtype) {
   if (T_tokens <= 0) return 0;
   if (H <= 0 || d <= 0 || r < 0 || rd < 0 || rd > r || (rd & 1) || R <= 0 || page_size <= 0 || (rd && !freq)) return TB_ERR_BAD_SIZE;
-  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::latent_prep_kernel<T>, dim3(T_tokens), dim3(128), 0, stream, proj, stride, kv_col, norm_w,
-                                      freq, positions, slots, (T*)k_cache, (T*)v_cache, q_out, H, d, r, rd, R, page_size, eps,
-                                      write_kv));
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::latent_prep_kernel<T>, dim3(T_tokens), dim3(128), 0, stream, q_in, q_stride, kv_in, kv_stride,
+                                      norm_w, freq, positions, slots, (T*)k_cache, (T*)v_cache, q_out, H, d, r, rd, R, page_size, eps,
+                                      write_kv, interleaved, mag));
 }
 
 // x_dtype / w_dtype / out_dtype: TB_F32 or TB_BF16 (x and out float32 with either weight type; x bfloat16 with bfloat16 weights).
@@ -182,13 +178,14 @@ int tb_head_linear(void* stream, const void* x, int x_dtype, long long x_stride,
   return TB_ERR_BAD_DTYPE;
 }
 
-int tb_sigmoid_gate(void* stream, const float* o, const float* g, int g_stride, void* y, int T_tokens, int N, int dtype) {
+int tb_sigmoid_gate(void* stream, const float* o, const float* g, int g_stride, void* y, int T_tokens, int N, int per, int dtype) {
   const long long total = (long long)T_tokens * N;
   if (total <= 0) return 0;
+  if (per <= 0 || N % per) return TB_ERR_BAD_SIZE;
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   TB_DISPATCH_DTYPE(dtype, tb::launch(tb::sigmoid_gate_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, o, g, g_stride, (T*)y,
-                                      total, N));
+                                      total, N, per));
 }
 
 }  // extern "C"

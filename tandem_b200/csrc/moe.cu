@@ -4,6 +4,10 @@
 //   chosen = the `top` largest s, found as the `top` largest z (the lower index wins a tie);  w_k = s_k / (sum of the chosen s + 1e-20) * scale
 //   y = sum_k w_k * W_down[e_k] (SiLU(W_gate[e_k] x) * (W_up[e_k] x))
 //
+// Options: a bias per router output that enters the CHOICE only (chosen = the largest s + bias; the weights stay s);
+// experts without a gate, W_down[e] act(W_up[e] x) with the exact GELU; and *identity experts*: router outputs
+// from `real` on stand for experts that return their input, so their slots add w_k x and touch no weights.
+//
 // `route` takes the logits to (expert, weight) pairs, one warp per token.  A (token, k) pair is a *slot*.
 // `expert_gate_up` computes the activated hidden row of every slot, `expert_down` its output row, `combine_slots`
 // the weighted sum of a token's slots in slot order: no atomics, and a token's result does not depend on the
@@ -26,8 +30,8 @@ constexpr int ROUTE_WARPS = 4;
 
 // logits float32 [T, E] -> ids int32 [T, top], weights float32 [T, top].  score: 0 sigmoid, 1 softmax.
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
-route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ weights, int T_tokens, int E, int top,
-             int score, int normalize, float scale) {
+route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ weights,
+             int T_tokens, int E, int top, int score, int normalize, float scale) {
   extern __shared__ float smem[];  // ROUTE_WARPS * E scores
   pdl_launch_dependents();
   pdl_wait();
@@ -46,6 +50,9 @@ route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __r
     for (int e = lane; e < E; e += 32) sum += expf(z[e] - m);
     sum = warp_sum(sum);
   }
+  // With a bias the choice is made on score + bias instead (the score itself stays the weight).
+  if (bias)
+    for (int e = lane; e < E; e += 32) s[e] = (score == 1 ? expf(z[e] - m) / sum : 1.f / (1.f + expf(-z[e]))) + bias[e];
   __syncwarp();
   float total = 0.f;
   for (int k = 0; k < top; ++k) {
@@ -59,7 +66,9 @@ route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __r
       const int oa = __shfl_xor_sync(0xffffffffu, at, o);
       if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
     }
-    const float sc = score == 1 ? expf(best - m) / sum : 1.f / (1.f + expf(-best));
+    if (at >= E) at = 0;  // nothing left to choose from (every score a NaN): no index beyond the row is handed on
+    const float zb = bias ? z[at] : best;  // every lane holds the same `at` after the exchange
+    const float sc = score == 1 ? expf(zb - m) / sum : 1.f / (1.f + expf(-zb));
     if (lane == 0) {
       ids[(size_t)t * top + k] = at;
       weights[(size_t)t * top + k] = sc;
@@ -169,12 +178,13 @@ constexpr int EX_PER_WARP = 4;  // outputs a warp computes one after the other: 
 template <typename X, typename W>
 __global__ void __launch_bounds__(256)
 expert_gate_up_kernel(const X* __restrict__ x, const W* __restrict__ w, const int* __restrict__ ids, const int* __restrict__ order,
-                      X* __restrict__ act, int top, int F, int K) {
+                      X* __restrict__ act, int top, int F, int K, int real) {
   extern __shared__ float xs[];  // K floats
   pdl_launch_dependents();
   pdl_wait();
   const int slot = order ? order[blockIdx.y] : blockIdx.y, t = slot / top;  // in `order`, slots of one expert run side by side
   const int e = ids[slot];
+  if (e >= real) return;  // an identity expert: the combine takes the token's own row
   const X* xr = x + (size_t)t * K;
   for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_float(xr[k]);
   __syncthreads();
@@ -189,15 +199,47 @@ expert_gate_up_kernel(const X* __restrict__ x, const W* __restrict__ w, const in
   }
 }
 
+__device__ __forceinline__ float gelu_exact(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752f)); }
+
+// Experts without a gate: act[slot, j] = GELU(x_t . up[e][j]), up [E, F, K].  grid (ceil(F / 32), slots).
+template <typename X, typename W>
+__global__ void __launch_bounds__(256)
+expert_up_kernel(const X* __restrict__ x, const W* __restrict__ w, const int* __restrict__ ids, const int* __restrict__ order,
+                 X* __restrict__ act, int top, int F, int K, int real) {
+  extern __shared__ float xs[];  // K floats
+  pdl_launch_dependents();
+  pdl_wait();
+  const int slot = order ? order[blockIdx.y] : blockIdx.y, t = slot / top;
+  const int e = ids[slot];
+  if (e >= real) return;
+  const X* xr = x + (size_t)t * K;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_float(xr[k]);
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const W* we = w + (size_t)e * F * K;
+  for (int i = 0; i < EX_PER_WARP; i += 2) {
+    const int j0 = (blockIdx.x * EX_PER_WARP + i) * 8 + warp, j1 = j0 + 8;
+    if (j0 >= F) return;
+    float d0, d1 = 0.f;
+    if (j1 < F) dot_rows2<W>(xs, we + (size_t)j0 * K, we + (size_t)j1 * K, K, lane, d0, d1);
+    else d0 = dot_row<W>(xs, we + (size_t)j0 * K, K, lane);
+    if (lane == 0) {
+      act[(size_t)slot * F + j0] = from_float<X>(gelu_exact(d0));
+      if (j1 < F) act[(size_t)slot * F + j1] = from_float<X>(gelu_exact(d1));
+    }
+  }
+}
+
 // grid (ceil(N / 32), slots): part[slot, n] = act[slot] . down[e][n]; the combine adds a token's slots in slot order.
 template <typename X, typename W>
 __global__ void __launch_bounds__(256)
 expert_down_kernel(const X* __restrict__ act, const W* __restrict__ w, const int* __restrict__ ids, const int* __restrict__ order,
-                   float* __restrict__ part, int N, int F) {
+                   float* __restrict__ part, int N, int F, int real) {
   extern __shared__ float as[];  // F floats
   pdl_launch_dependents();
   pdl_wait();
   const int slot = order ? order[blockIdx.y] : blockIdx.y;
+  if (ids[slot] >= real) return;
   for (int i = threadIdx.x; i < F; i += blockDim.x) as[i] = to_float(act[(size_t)slot * F + i]);
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -223,9 +265,11 @@ constexpr int ET_M = 64, ET_N = 64, ET_K = 32, ET_PAD = 8;
 // list with offsets rounded up to whole tiles of ET_M (rows that pad a tile hold -1), and lists the slots of an
 // expert in ascending slot order.  offsets int32 [E + 1]; sorted int32 [capacity], capacity >= slots + E * (ET_M - 1).
 // With tile_group (int32 [capacity / tile_rows]) every tile of tile_rows rows also learns its expert (-1: the tile lies
-// behind the last expert's rows), and with position (int32 [slots]) every slot its row in the sorted list.
+// behind the last expert's rows, or belongs to an identity expert: e >= real), and with position (int32 [slots])
+// every slot its row in the sorted list.
 __global__ void sort_slots_kernel(const int* __restrict__ ids, int* __restrict__ offsets, int* __restrict__ sorted, int slots,
-                                  int E, int capacity, int tile_rows, int* __restrict__ tile_group, int* __restrict__ position) {
+                                  int E, int capacity, int tile_rows, int* __restrict__ tile_group, int* __restrict__ position,
+                                  int real) {
   extern __shared__ int sm[];  // E counts, then E + 1 offsets
   pdl_launch_dependents();
   pdl_wait();
@@ -253,7 +297,7 @@ __global__ void sort_slots_kernel(const int* __restrict__ ids, int* __restrict__
         e = 0;
         while (e + 1 < E && off[e + 1] <= i * tile_rows) ++e;
       }
-      tile_group[i] = e;
+      tile_group[i] = e < real ? e : -1;  // identity experts are the last ones: their tiles are passed over
     }
   __syncthreads();
   // expert by expert, a warp lists its expert's slots in ascending order (ballot + prefix over runs of 32 slots)
@@ -280,14 +324,16 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, const uint
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-// A tile of ET_M sorted rows x ET_N outputs of one expert.  GATED: outputs are SiLU(gate) * up for ET_N hidden
+// A tile of ET_M sorted rows x ET_N outputs of one expert.  MODE 1 (gated): outputs are SiLU(gate) * up for ET_N hidden
 // columns (both weight tiles are multiplied), rows are gathered from x by token = slot / top, and the result goes to
-// act[sorted position]; else: rows are act[sorted position], the result (float32) goes to part[slot].
+// act[sorted position]; MODE 2 (no gate): the same with one weight tile and GELU; MODE 0: rows are act[sorted position],
+// the result (float32) goes to part[slot].  Tiles of identity experts (e >= real) are passed over.
 // 128 threads = 4 warps, warp w owns rows 16 w .. 16 w + 15 of the tile and all ET_N columns.
-template <bool GATED>
+template <int MODE>
 __global__ void __launch_bounds__(128)
 expert_tiles_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, const int* __restrict__ offsets,
-                    const int* __restrict__ sorted, void* __restrict__ out, int top, int E, int N, int K) {
+                    const int* __restrict__ sorted, void* __restrict__ out, int top, int E, int N, int K, int real) {
+  constexpr bool GATED = MODE == 1, GATHER = MODE != 0;
   __shared__ __align__(16) __nv_bfloat16 As[ET_M][ET_K + ET_PAD];
   __shared__ __align__(16) __nv_bfloat16 Bs[GATED ? 2 : 1][ET_N][ET_K + ET_PAD];
   __shared__ int row_src[ET_M];
@@ -297,11 +343,12 @@ expert_tiles_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
   if (row0 >= offsets[E]) return;
   int e = 0;
   while (e + 1 < E && offsets[e + 1] <= row0) ++e;
+  if (e >= real) return;
   const int n0 = blockIdx.x * ET_N;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid < ET_M) {
     const int slot = sorted[row0 + tid];
-    row_src[tid] = slot < 0 ? -1 : (GATED ? slot / top : row0 + tid);
+    row_src[tid] = slot < 0 ? -1 : (GATHER ? slot / top : row0 + tid);
   }
   __syncthreads();
   const __nv_bfloat16* we = w + (size_t)e * (GATED ? 2 : 1) * N * K;
@@ -360,7 +407,11 @@ expert_tiles_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
       const int n = n0 + j * 8 + (lane & 3) * 2;
       const int slot = sorted[row0 + r];
       if (slot < 0 || n >= N) continue;
-      if (GATED) {
+      if (MODE == 2) {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)(row0 + r) * N + n;
+        o[0] = __float2bfloat16_rn(gelu_exact(acc[0][j][2 * half]));
+        if (n + 1 < N) o[1] = __float2bfloat16_rn(gelu_exact(acc[0][j][2 * half + 1]));
+      } else if (GATED) {
         const float g0 = acc[0][j][2 * half], g1 = acc[0][j][2 * half + 1];
         const float v0 = g0 / (1.f + expf(-g0)) * acc[GATED ? 1 : 0][j][2 * half];
         const float v1 = g1 / (1.f + expf(-g1)) * acc[GATED ? 1 : 0][j][2 * half + 1];
@@ -390,8 +441,11 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const in
 }
 
 // y[t, n] = sum_k weight[t, k] * part[row of slot t top + k, n], in slot order (position null: the slot's own row).
+// A slot of an identity expert (ids given and ids[slot] >= real) adds weight * x[t, n] instead.
+template <typename X>
 __global__ void combine_slots_kernel(const float* __restrict__ part, const float* __restrict__ weights, float* __restrict__ y,
-                                     long long total, int N, int top, const int* __restrict__ position) {
+                                     long long total, int N, int top, const int* __restrict__ position, const int* __restrict__ ids,
+                                     int real, const X* __restrict__ x) {
   pdl_launch_dependents();
   pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -399,6 +453,10 @@ __global__ void combine_slots_kernel(const float* __restrict__ part, const float
     const int n = (int)(i % N);
     float acc = 0.f;
     for (int k = 0; k < top; ++k) {
+      if (ids && ids[t * top + k] >= real) {
+        acc = fmaf(weights[t * top + k], to_float(x[i]), acc);
+        continue;
+      }
       const size_t row = position ? (size_t)position[t * top + k] : (size_t)t * top + k;
       acc = fmaf(weights[t * top + k], part[row * N + n], acc);
     }
@@ -410,35 +468,40 @@ __global__ void combine_slots_kernel(const float* __restrict__ part, const float
 
 extern "C" {
 
-int tb_moe_route(void* stream, const float* logits, int* ids, float* weights, int T_tokens, int E, int top, int score,
-                 int normalize, float scale) {
+// bias float32 [E] or null: the choice is made on score + bias, the weights are the scores.
+int tb_moe_route(void* stream, const float* logits, const float* bias, int* ids, float* weights, int T_tokens, int E, int top,
+                 int score, int normalize, float scale) {
   if (T_tokens <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || top > 32 || score < 0 || score > 1) return TB_ERR_BAD_SIZE;
   const size_t smem = (size_t)tb::ROUTE_WARPS * E * sizeof(float);
   if (smem > 48 * 1024) return TB_ERR_BAD_SIZE;
   return tb::launch(tb::route_kernel, dim3((T_tokens + tb::ROUTE_WARPS - 1) / tb::ROUTE_WARPS), dim3(tb::ROUTE_WARPS * 32), smem,
-                    stream, logits, ids, weights, T_tokens, E, top, score, normalize, scale);
+                    stream, logits, bias, ids, weights, T_tokens, E, top, score, normalize, scale);
 }
 
-// x [T, K], w [E, 2 F, K], act [T top, F] of the activations' type `dtype`; the weights of type `dtype` too.
+// x [T, K], act [T top, F] of the activations' type `dtype`; the weights of type `dtype` too: w [real, 2 F, K] (gate rows,
+// then up rows) with `gated`, else [real, F, K] and the exact GELU.  Slots whose expert is `real` or more are left out.
 // order: int32 [T top] (the slots sorted by expert, so that an expert's rows are fetched once for slots that share it) or null.
 int tb_moe_gate_up(void* stream, const void* x, const void* w, const int* ids, const int* order, void* act, int T_tokens, int top,
-                   int F, int K, int dtype) {
+                   int F, int K, int real, int gated, int dtype) {
   if (T_tokens <= 0) return 0;
   if (top <= 0 || F <= 0 || K <= 0 || (long long)T_tokens * top > 65535 || K * sizeof(float) > 48 * 1024) return TB_ERR_BAD_SIZE;
   const dim3 grid((F + 8 * tb::EX_PER_WARP - 1) / (8 * tb::EX_PER_WARP), T_tokens * top);
-  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::expert_gate_up_kernel<T, T>, grid, dim3(256), (size_t)K * sizeof(float), stream, (const T*)x,
-                                      (const T*)w, ids, order, (T*)act, top, F, K));
+  if (gated)
+    TB_DISPATCH_DTYPE(dtype, tb::launch(tb::expert_gate_up_kernel<T, T>, grid, dim3(256), (size_t)K * sizeof(float), stream,
+                                        (const T*)x, (const T*)w, ids, order, (T*)act, top, F, K, real));
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::expert_up_kernel<T, T>, grid, dim3(256), (size_t)K * sizeof(float), stream, (const T*)x,
+                                      (const T*)w, ids, order, (T*)act, top, F, K, real));
 }
 
-// act [T top, F], w [E, N, F] of type `dtype`; part float32 [T top, N].
+// act [T top, F], w [real, N, F] of type `dtype`; part float32 [T top, N].
 int tb_moe_down(void* stream, const void* act, const void* w, const int* ids, const int* order, float* part, int T_tokens, int top,
-                int N, int F, int dtype) {
+                int N, int F, int real, int dtype) {
   if (T_tokens <= 0) return 0;
   if (top <= 0 || F <= 0 || N <= 0 || (long long)T_tokens * top > 65535 || (size_t)F * sizeof(float) > 48 * 1024) return TB_ERR_BAD_SIZE;
   const dim3 grid((N + 8 * tb::EX_PER_WARP - 1) / (8 * tb::EX_PER_WARP), T_tokens * top);
   TB_DISPATCH_DTYPE(dtype, tb::launch(tb::expert_down_kernel<T, T>, grid, dim3(256), (size_t)F * sizeof(float), stream, (const T*)act,
-                                      (const T*)w, ids, order, part, N, F));
+                                      (const T*)w, ids, order, part, N, F, real));
 }
 
 // The slots sorted by expert, ascending within an expert: order int32 [T top] (offsets int32 [E + 1] is scratch).
@@ -446,50 +509,60 @@ int tb_moe_order(void* stream, const int* ids, int* offsets, int* order, int T_t
   if (T_tokens <= 0) return 0;
   if (top <= 0 || E <= 0 || E > 4096) return TB_ERR_BAD_SIZE;
   return tb::launch(tb::sort_slots_kernel, dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int), stream, ids, offsets, order,
-                    T_tokens * top, E, T_tokens * top, 1, (int*)nullptr, (int*)nullptr);
+                    T_tokens * top, E, T_tokens * top, 1, (int*)nullptr, (int*)nullptr, E);
 }
 
 int tb_moe_tile_rows() { return tb::ET_M; }
 
+static int combine(void* stream, const float* part, const float* weights, const int* position, float* y, int T_tokens, int top, int N,
+                   const int* ids, int real, const void* x, int x_dtype) {
+  const long long total = (long long)T_tokens * N;
+  if (total <= 0) return 0;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  TB_DISPATCH_DTYPE(x_dtype, tb::launch(tb::combine_slots_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, part, weights, y, total, N,
+                                        top, position, ids, real, (const T*)x));
+}
+
 // The tensor-core path (bfloat16).  offsets int32 [E + 1], sorted int32 [capacity] and act bfloat16 [capacity, F]
 // and part float32 [T top, N] are scratch of the caller; capacity = T top + E (tile rows - 1) rounded up to whole tiles.
+// E counts every router output; the weights hold the first `real` experts, the others are identity experts.
 int tb_moe_tiles(void* stream, const void* x, const void* w_gate_up, const void* w_down, const int* ids, const float* weights,
                  int* offsets, int* sorted, void* act, float* part, float* y, int T_tokens, int top, int E, int N, int F, int K,
-                 int capacity) {
+                 int capacity, int real, int gated) {
   if (T_tokens <= 0) return 0;
   const int slots = T_tokens * top;
   if (top <= 0 || E <= 0 || E > 4096 || (F & 7) || (K & 7) || N != K || capacity % tb::ET_M || capacity < slots + E * (tb::ET_M - 1))
     return TB_ERR_BAD_SIZE;
   int rc = tb::launch(tb::sort_slots_kernel, dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int), stream, ids, offsets, sorted,
-                      slots, E, capacity, (int)tb::ET_M, (int*)nullptr, (int*)nullptr);
+                      slots, E, capacity, (int)tb::ET_M, (int*)nullptr, (int*)nullptr, real);
   if (rc != 0) return rc;
   const int row_tiles = capacity / tb::ET_M;
-  rc = tb::launch(tb::expert_tiles_kernel<true>, dim3((F + tb::ET_N - 1) / tb::ET_N, row_tiles), dim3(128), 0, stream,
-                  (const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gate_up, offsets, sorted, act, top, E, F, K);
+  const dim3 up_grid((F + tb::ET_N - 1) / tb::ET_N, row_tiles);
+  rc = gated ? tb::launch(tb::expert_tiles_kernel<1>, up_grid, dim3(128), 0, stream, (const __nv_bfloat16*)x,
+                          (const __nv_bfloat16*)w_gate_up, offsets, sorted, act, top, E, F, K, real)
+             : tb::launch(tb::expert_tiles_kernel<2>, up_grid, dim3(128), 0, stream, (const __nv_bfloat16*)x,
+                          (const __nv_bfloat16*)w_gate_up, offsets, sorted, act, top, E, F, K, real);
   if (rc != 0) return rc;
-  rc = tb::launch(tb::expert_tiles_kernel<false>, dim3((N + tb::ET_N - 1) / tb::ET_N, row_tiles), dim3(128), 0, stream,
-                  (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, offsets, sorted, part, top, E, N, F);
+  rc = tb::launch(tb::expert_tiles_kernel<0>, dim3((N + tb::ET_N - 1) / tb::ET_N, row_tiles), dim3(128), 0, stream,
+                  (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, offsets, sorted, part, top, E, N, F, real);
   if (rc != 0) return rc;
-  const long long total = (long long)T_tokens * N;
-  long long blocks = (total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  return tb::launch(tb::combine_slots_kernel, dim3((int)blocks), dim3(256), 0, stream, part, weights, y, total, N, top,
-                    (const int*)nullptr);
+  return combine(stream, part, weights, nullptr, y, T_tokens, top, N, real < E ? ids : nullptr, real, x, TB_BF16);
 }
 
 // The front and the back of the path that runs the experts as grouped products of 128-row tiles on tcgen05 (the
 // package's wide product in its grouped form): `moe_sort_gather` sorts the slots by expert (offsets padded to whole
-// tiles), names every tile's expert, remembers every slot's row and copies the tokens' rows into sorted order;
-// `moe_combine` adds a token's slots, each from its row, in slot order.  xs bfloat16 [capacity, K]; capacity a multiple
-// of tile_rows and >= T top + E (tile_rows - 1).
+// tiles), names every tile's expert (-1 for identity experts), remembers every slot's row and copies the tokens' rows
+// into sorted order; `moe_combine` adds a token's slots, each from its row, in slot order.  xs bfloat16 [capacity, K];
+// capacity a multiple of tile_rows and >= T top + E (tile_rows - 1).
 int tb_moe_sort_gather(void* stream, const void* x, const int* ids, int* offsets, int* sorted, int* tile_group, int* position,
-                       void* xs, int T_tokens, int top, int E, int K, int capacity, int tile_rows) {
+                       void* xs, int T_tokens, int top, int E, int K, int capacity, int tile_rows, int real) {
   if (T_tokens <= 0) return 0;
   const int slots = T_tokens * top;
   if (top <= 0 || E <= 0 || E > 4096 || (K & 7) || tile_rows <= 0 || capacity % tile_rows || capacity < slots + E * (tile_rows - 1))
     return TB_ERR_BAD_SIZE;
   int rc = tb::launch(tb::sort_slots_kernel, dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int), stream, ids, offsets, sorted,
-                      slots, E, capacity, tile_rows, tile_group, position);
+                      slots, E, capacity, tile_rows, tile_group, position, real);
   if (rc != 0) return rc;
   long long blocks = ((long long)capacity * (K >> 3) + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
@@ -497,12 +570,10 @@ int tb_moe_sort_gather(void* stream, const void* x, const int* ids, int* offsets
                     (__nv_bfloat16*)xs, capacity, K, top);
 }
 
-int tb_moe_combine(void* stream, const float* part, const float* weights, const int* position, float* y, int T_tokens, int top, int N) {
-  const long long total = (long long)T_tokens * N;
-  if (total <= 0) return 0;
-  long long blocks = (total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  return tb::launch(tb::combine_slots_kernel, dim3((int)blocks), dim3(256), 0, stream, part, weights, y, total, N, top, position);
+// ids / real / x (of type x_dtype) only where there are identity experts (ids null: none).
+int tb_moe_combine(void* stream, const float* part, const float* weights, const int* position, float* y, int T_tokens, int top, int N,
+                   const int* ids, int real, const void* x, int x_dtype) {
+  return combine(stream, part, weights, position, y, T_tokens, top, N, ids, real, x, x_dtype);
 }
 
 }  // extern "C"

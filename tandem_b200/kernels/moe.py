@@ -1,4 +1,5 @@
-"""Entry points of ``csrc/moe.cu``: routing by score, and the chosen experts' gated feed-forwards.
+"""Entry points of ``csrc/moe.cu``: routing by score, and the chosen experts' feed-forwards (gated with SiLU,
+or plain with the exact GELU; router outputs beyond the real experts may stand for identity experts).
 
 ``route`` turns float32 router logits into (expert, weight) pairs.  ``experts`` runs the chosen
 experts of every token over stacked weights: one warp per output element for steps of few tokens
@@ -11,6 +12,7 @@ captured in a CUDA graph.
 from __future__ import annotations
 
 import ctypes
+from typing import Optional
 
 import torch
 
@@ -24,19 +26,25 @@ WIDE_TILE = 128
 _MAX_SLOTS = 65535  # slots per launch of the one-warp-per-output kernels
 
 
-def route(logits: torch.Tensor, top_k: int, score: str, normalize: bool, scale: float) -> tuple:
+def route(logits: torch.Tensor, top_k: int, score: str, normalize: bool, scale: float,
+          choice_bias: Optional[torch.Tensor] = None) -> tuple:
     """logits float32 [T, E] -> (experts int32 [T, top_k], weights float32 [T, top_k]): scores sigmoid(z) or
     softmax(z), the ``top_k`` largest chosen (the lower index wins a tie), their scores divided by their sum
-    (+ 1e-20) where ``normalize``, times ``scale``."""
+    (+ 1e-20) where ``normalize``, times ``scale``.  ``choice_bias`` float32 [E]: the choice is made on score + bias;
+    the weights are the scores without it."""
     ops._need(logits, "logits", torch.float32)
+    if choice_bias is not None:
+        ops._need(choice_bias, "choice_bias", torch.float32)
+        if choice_bias.numel() != logits.shape[1]:
+            raise ops.KernelError(f"a choice bias of {choice_bias.numel()} entries for {logits.shape[1]} router outputs")
     if score not in _SCORES:
         raise ops.KernelError(f"no score {score!r} (have {sorted(_SCORES)})")
     T, E = logits.shape
     ids = torch.empty((T, top_k), dtype=torch.int32, device=logits.device)
     weights = torch.empty((T, top_k), dtype=torch.float32, device=logits.device)
     lib = load_library("moe")
-    ops._check(lib.tb_moe_route(ops._stream(), ops._ptr(logits), ops._ptr(ids), ops._ptr(weights), T, E, top_k, _SCORES[score],
-                                int(bool(normalize)), ctypes.c_float(scale)), "moe_route")
+    ops._check(lib.tb_moe_route(ops._stream(), ops._ptr(logits), ops._ptr(choice_bias), ops._ptr(ids), ops._ptr(weights), T, E, top_k,
+                                _SCORES[score], int(bool(normalize)), ctypes.c_float(scale)), "moe_route")
     return ids, weights
 
 
@@ -53,11 +61,11 @@ def wide_applies(x: torch.Tensor, hidden: int, inner: int, top: int, num_experts
             and ops.env("TANDEM_MOE", "wide") not in ("simt", "tiles"))
 
 
-def _experts_wide(x, gate_up, down, ids, weights) -> torch.Tensor:
+def _experts_wide(x, gate_up, down, ids, weights, gated: bool, E: int) -> torch.Tensor:
     from tandem_b200.kernels import gemm_bf16
 
     T, K = x.shape
-    E, F, top = gate_up.shape[0], gate_up.shape[1] // 2, ids.shape[1]
+    real, F, top = gate_up.shape[0], down.shape[2], ids.shape[1]
     capacity = -(-(T * top + E * (WIDE_TILE - 1)) // WIDE_TILE) * WIDE_TILE
     dev = x.device
     offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
@@ -67,32 +75,46 @@ def _experts_wide(x, gate_up, down, ids, weights) -> torch.Tensor:
     xs = torch.empty((capacity, K), dtype=torch.bfloat16, device=dev)
     lib = load_library("moe")
     ops._check(lib.tb_moe_sort_gather(ops._stream(), ops._ptr(x), ops._ptr(ids), ops._ptr(offsets), ops._ptr(order), ops._ptr(tile_group),
-                                      ops._ptr(position), ops._ptr(xs), T, top, E, K, capacity, WIDE_TILE), "moe_sort_gather")
+                                      ops._ptr(position), ops._ptr(xs), T, top, E, K, capacity, WIDE_TILE, real), "moe_sort_gather")
     ops.launches += 1  # two kernels
-    act = gemm_bf16.wide_grouped(xs, gate_up.view(E * 2 * F, K), tile_group, E, torch.bfloat16, gated=True)
-    part = gemm_bf16.wide_grouped(act, down.view(E * K, F), tile_group, E, torch.float32, gated=False)
+    if gated:
+        act = gemm_bf16.wide_grouped(xs, gate_up.view(real * 2 * F, K), tile_group, real, torch.bfloat16, gated=True)
+    else:
+        act = gemm_bf16.wide_grouped(xs, gate_up.view(real * F, K), tile_group, real, torch.bfloat16, activation="gelu")
+    part = gemm_bf16.wide_grouped(act, down.view(real * K, F), tile_group, real, torch.float32, gated=False)
     y = torch.empty((T, K), dtype=torch.float32, device=dev)
-    ops._check(lib.tb_moe_combine(ops._stream(), ops._ptr(part), ops._ptr(weights), ops._ptr(position), ops._ptr(y), T, top, K),
-               "moe_combine")
+    _combine(lib, part, weights, position, y, T, top, K, ids, real, E, x)
     return y
 
 
-def experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+def _combine(lib, part, weights, position, y, T: int, top: int, N: int, ids, real: int, E: int, x) -> None:
+    """y[t] = the weighted sum of a token's slots; slots of identity experts (``real`` <= expert < ``E``) add weight * x[t]."""
+    identity = real < E
+    ops._check(lib.tb_moe_combine(ops._stream(), ops._ptr(part), ops._ptr(weights), ops._ptr(position), ops._ptr(y), T, top, N,
+                                  ops._ptr(ids if identity else None), real, ops._ptr(x if identity else None), ops._code(x.dtype)),
+               "moe_combine")
+
+
+def experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+            gated: bool = True, num_router_outputs: Optional[int] = None) -> torch.Tensor:
     """sum_k weights[t, k] * down[e] (SiLU(gate[e] x_t) * (up[e] x_t)) with e = ids[t, k]: float32 [T, hidden].
-    x [T, hidden]; gate_up [E, 2 F, hidden] (an expert's gate rows, then its up rows); down [E, hidden, F]."""
+    x [T, hidden]; gate_up [E, 2 F, hidden] (an expert's gate rows, then its up rows); down [E, hidden, F].
+    Without a gate (``gated`` False): ``gate_up`` is up [E, F, hidden] and an expert is down[e] GELU(up[e] x_t), the
+    exact GELU.  ``num_router_outputs`` > E: experts E and above are identity experts, whose slots add weights[t, k] * x_t."""
     ops._need(x, "x")
     ops._need(gate_up, "gate_up", x.dtype)
     ops._need(down, "down", x.dtype)
     ops._need(ids, "ids", torch.int32)
     ops._need(weights, "weights", torch.float32)
     T, K = x.shape
-    E, F2, K2 = gate_up.shape
-    F, top = F2 // 2, ids.shape[1]
-    if K2 != K or tuple(down.shape) != (E, K, F) or tuple(ids.shape) != (T, top) or tuple(weights.shape) != (T, top):
+    real, F2, K2 = gate_up.shape
+    F, top = (F2 // 2 if gated else F2), ids.shape[1]
+    E = real if num_router_outputs is None else int(num_router_outputs)
+    if K2 != K or tuple(down.shape) != (real, K, F) or tuple(ids.shape) != (T, top) or tuple(weights.shape) != (T, top) or E < real:
         raise ops.KernelError(f"x {tuple(x.shape)}, gate_up {tuple(gate_up.shape)}, down {tuple(down.shape)}, ids "
                               f"{tuple(ids.shape)} do not fit together")
     if wide_applies(x, K, F, top, E):
-        return _experts_wide(x, gate_up, down, ids, weights)
+        return _experts_wide(x, gate_up, down, ids, weights, gated, E)
     y = torch.empty((T, K), dtype=torch.float32, device=x.device)
     lib = load_library("moe")
     if tiles_apply(x, K, F):
@@ -104,7 +126,7 @@ def experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: tor
         part = torch.empty((T * top, K), dtype=torch.float32, device=x.device)
         ops._check(lib.tb_moe_tiles(ops._stream(), ops._ptr(x), ops._ptr(gate_up), ops._ptr(down), ops._ptr(ids), ops._ptr(weights),
                                     ops._ptr(offsets), ops._ptr(order), ops._ptr(act), ops._ptr(part), ops._ptr(y), T, top, E, K, F, K,
-                                    capacity), "moe_tiles")
+                                    capacity, real, int(bool(gated))), "moe_tiles")
         ops.launches += 3  # four kernels
         return y
     step = max(1, _MAX_SLOTS // top)
@@ -116,9 +138,8 @@ def experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: tor
         part = torch.empty((n * top, K), dtype=torch.float32, device=x.device)
         ops._check(lib.tb_moe_order(ops._stream(), ops._ptr(ids[t0:]), ops._ptr(offsets), ops._ptr(order), n, top, E), "moe_order")
         ops._check(lib.tb_moe_gate_up(ops._stream(), ops._ptr(x[t0:]), ops._ptr(gate_up), ops._ptr(ids[t0:]), ops._ptr(order),
-                                      ops._ptr(act), n, top, F, K, ops._code(x.dtype)), "moe_gate_up")
+                                      ops._ptr(act), n, top, F, K, real, int(bool(gated)), ops._code(x.dtype)), "moe_gate_up")
         ops._check(lib.tb_moe_down(ops._stream(), ops._ptr(act), ops._ptr(down), ops._ptr(ids[t0:]), ops._ptr(order), ops._ptr(part),
-                                   n, top, K, F, ops._code(x.dtype)), "moe_down")
-        ops._check(lib.tb_moe_combine(ops._stream(), ops._ptr(part), ops._ptr(weights[t0:]), ops._ptr(None), ops._ptr(y[t0:]), n, top, K),
-                   "moe_combine")
+                                   n, top, K, F, real, ops._code(x.dtype)), "moe_down")
+        _combine(lib, part, weights[t0:], None, y[t0:], n, top, K, ids[t0:], real, E, x[t0:])
     return y

@@ -50,6 +50,11 @@ class Decoder:
         params: dict[str, ParamSpec] = {"embedding": ParamSpec((e.vocab_size, e.hidden_size), (WeightSource(e.weight),))}
         if e.positions is not None:
             params["positions"] = ParamSpec((plan.max_position, e.hidden_size), (WeightSource(e.positions),))
+        if e.norm is not None:
+            if not hasattr(part("norm", e.norm.kind), "in_place"):
+                raise ConfigError(f"the norm {e.norm.kind!r} cannot norm the embedded rows in place")
+            for local, ps in part("norm", e.norm.kind).params(e.norm).items():
+                params[f"embedding_norm.{local}"] = ps
         for i, layer in enumerate(plan.layers):
             check_slots(i, layer, part("block", layer.block))
             for slot, family, spec in layer.parts:
@@ -67,6 +72,9 @@ class Decoder:
         self.embedding = tensors["embedding"]
         self.positions = tensors.get("positions")
         self.head = tensors.get("head", self.embedding)  # tied: llama_family.py:108
+        self.embedding_norm = None
+        if e.norm is not None:
+            self.embedding_norm = part("norm", e.norm.kind)(e.norm, weights_of("embedding_norm."), dtype, self.device)
         self.layers = []
         for i, layer in enumerate(plan.layers):
             built = {}
@@ -120,6 +128,8 @@ class Decoder:
             return torch.empty((0, h.vocab_size), dtype=torch.float32, device=self.device)
         residual = ops.embedding(ctx.token_ids, self.embedding, scale=e.scale, positions=ctx.positions,
                                  position_table=self.positions, copies=e.copies)
+        if self.embedding_norm is not None:
+            self.embedding_norm.in_place(residual)
         x = None
         for r, run in enumerate(self.plan.order):
             ctx.run = r

@@ -1,11 +1,12 @@
 """The built-in parts, registered by kind."""
 
 from tandem_b200.parts.attention import PagedAttention
-from tandem_b200.parts.block import ConnectedBlock, ParallelBlock, PreNormBlock
-from tandem_b200.parts.connection import StreamLink
+from tandem_b200.parts.block import ConnectedBlock, ParallelBlock, PostNormBlock, PreNormBlock
+from tandem_b200.parts.connection import DepthAverage, StreamLink
+from tandem_b200.parts.convolution import ShortConvolution
 from tandem_b200.parts.latent_attention import LatentAttention
 from tandem_b200.parts.mlp import DenseMLP, GatedMLP, RoutedMLP
-from tandem_b200.parts.norm import RMSNorm
+from tandem_b200.parts.norm import GroupRMSNorm, RMSNorm
 from tandem_b200.parts.recurrence import DecayRecurrence, SelectiveRecurrence
 from tandem_b200.parts.rope import NoPosition, RotaryTable
 from tandem_b200.parts.sink_attention import SinkAttention
@@ -26,3 +27,7 @@ register_part("mixer", "latent_attention", LatentAttention)
 register_part("feed_forward", "routed_mlp", RoutedMLP)
 register_part("connection", "stream_link", StreamLink)
 register_part("block", "connected", ConnectedBlock)
+register_part("norm", "group_rmsnorm", GroupRMSNorm)
+register_part("mixer", "short_convolution", ShortConvolution)
+register_part("connection", "depth_average", DepthAverage)
+register_part("block", "postnorm", PostNormBlock)

@@ -13,6 +13,11 @@ by a link of its own (``parts/connection.py``): u = norm(read of the streams); y
 the streams are rewritten from themselves and y.  The write is left pending and done by the next
 norm's kernel, so every "write, read, normalise" is one launch.  The feed-forward may be absent.
 
+"postnorm": the norms sit on the sublayers' OUTPUT, x <- x + norm(mixer(x)); x <- x + norm(feed_forward(x)), all
+on one float32 stream.  Optional parts: a short convolution in front of either sublayer (the sublayer reads
+x + conv(x)), and a depth average behind the layer (what is handed on is a weighted sum of the results of all
+layers so far).  One kernel per boundary does "norm, add, [average,] convolution"; the feed-forward may be absent.
+
 An arrangement declares the parts it works with as ``slots`` (slot name -> family; all needed)
 and ``optional_slots``; the decoder builds what the layer's spec lists under those names and
 hands the arrangement a layer whose attributes they are.  ``forward(layer, x, residual, ctx)``
@@ -103,3 +108,50 @@ class ConnectedBlock:
             h = layer.feed_forward_norm.forward(x, residual, ctx.dtype, read=layer.feed_forward_link.read)
             x = layer.feed_forward_link.write(deferred.tensor(layer.feed_forward.forward(h, ctx)))
         return x
+
+
+class PostNormBlock:
+    """Norms behind the sublayers.  Everything is in the stream when the layer returns (it returns None)."""
+
+    slots = {"mixer": "mixer", "mixer_norm": "norm"}
+    optional_slots = {"feed_forward": "feed_forward", "feed_forward_norm": "norm", "mixer_conv": "mixer",
+                      "feed_forward_conv": "mixer", "average": "connection"}
+    BUFFER = "postnorm.second_stream"
+
+    @staticmethod
+    def _float32(y) -> torch.Tensor:
+        y = deferred.tensor(y)
+        return y if y.dtype == torch.float32 else y.float()
+
+    def forward(self, layer, x, residual: torch.Tensor, ctx: StepContext):
+        from tandem_b200.kernels import ops, post_norm
+
+        if x is not None:  # an arrangement of another kind in front left its last output outside the stream
+            ops.add_pair(residual, self._float32(x))
+        conv1, conv2 = getattr(layer, "mixer_conv", None), getattr(layer, "feed_forward_conv", None)
+        average, ff = getattr(layer, "average", None), getattr(layer, "feed_forward", None)
+        planes = average.results(ctx, residual) if average is not None else None
+        tail = dict(planes=planes, coeff=average.coeff, n_planes=average.count - 1) if average is not None else {}
+        if conv1 is not None:
+            h = conv1.forward(residual, ctx)
+        else:
+            h = residual if ctx.dtype == torch.float32 else post_norm.short_conv(residual, None, None, ctx, ctx.dtype)
+        y = self._float32(layer.mixer.forward(h, ctx))
+        n1 = layer.mixer_norm
+        if ff is None:
+            post_norm.link(residual, y, n1.weight, n1.groups, n1.eps, residual, **tail)
+            return None
+        second = ctx.scratch.get(self.BUFFER)
+        if second is None or second.shape != residual.shape:
+            second = ctx.scratch[self.BUFFER] = torch.empty_like(residual)
+        if conv2 is not None:
+            h = post_norm.link(residual, y, n1.weight, n1.groups, n1.eps, second, taps=conv2.taps, state=conv2.state(ctx), ctx=ctx,
+                               out_dtype=ctx.dtype)
+            conv2.keep(second, ctx)
+        else:
+            post_norm.link(residual, y, n1.weight, n1.groups, n1.eps, second)
+            h = second if ctx.dtype == torch.float32 else post_norm.short_conv(second, None, None, ctx, ctx.dtype)
+        y = self._float32(ff.forward(h, ctx))
+        n2 = layer.feed_forward_norm
+        post_norm.link(second, y, n2.weight, n2.groups, n2.eps, residual, **tail)
+        return None

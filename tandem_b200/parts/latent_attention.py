@@ -8,8 +8,9 @@ of latent_dim + rotary_dim numbers over one key head whose values are the latent
 is the package's attention kernel for keys and values of different sizes (one warp per token and
 head in float32, query tiles on the tensor cores for prompt portions and split keys for single
 tokens in bfloat16), with no window, cap, bias or sink.  One fused projection (rows [q | down-projection
-| gate]) with a float32 result; the gate multiplies the concatenated heads by sigmoid of its own
-projection of the mixer's input.
+| gate]) with a float32 result; the gate multiplies the concatenated heads (or every head by one number)
+by sigmoid of its own projection of the mixer's input.  Where the queries come through a latent of their
+own, the fused projection's first rows make that latent, which is normed and expanded by a second product.
 """
 
 from __future__ import annotations
@@ -18,13 +19,15 @@ import torch
 
 from tandem_b200.cache.manager import KVNeed
 from tandem_b200.config.model_config import ConfigError
-from tandem_b200.config.plan import LatentAttentionSpec, ParamSpec, WeightSource
+from tandem_b200.config.plan import LatentAttentionSpec, ParamSpec, WeightSource, rotary_table
 from tandem_b200.kernels import deferred, ops
 from tandem_b200.kernels import latent_attention as kernels
+from tandem_b200.kernels import post_norm
 from tandem_b200.kernels import sink_attention as attention
 from tandem_b200.parts.base import Mixer, StepContext
 
-_SUFFIX = {"q": "q", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "g": "g", "o": "o"}
+_SUFFIX = {"q": "q", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "g": "g", "o": "o", "dq": "dq",
+           "dq_norm": "dq.norm", "uq": "uq"}
 
 
 def _name(spec, local: str) -> str:
@@ -35,19 +38,28 @@ class LatentAttention(Mixer):
     capturable = True  # forward only launches kernels and reads the batch from device arrays
 
     @staticmethod
-    def params(spec: LatentAttentionSpec) -> dict:
+    def gate_rows(spec: LatentAttentionSpec) -> int:
+        return {"sigmoid": spec.num_heads * spec.value_dim, "sigmoid_head": spec.num_heads}.get(spec.gate, 0)
+
+    @classmethod
+    def params(cls, spec: LatentAttentionSpec) -> dict:
         H, W = spec.num_heads, spec.hidden_size
-        q, kv, g = H * (spec.head_dim + spec.rotary_dim), spec.latent_dim + spec.rotary_dim, H * spec.value_dim
-        sources = [WeightSource(_name(spec, "q"), 0, q), WeightSource(_name(spec, "dkv"), q, kv)]
-        if spec.gate != "none":
-            sources.append(WeightSource(_name(spec, "g"), q + kv, g))
-        return {
-            "in": ParamSpec((q + kv + (g if spec.gate != "none" else 0), W), tuple(sources)),
+        q, kv, g = H * (spec.head_dim + spec.rotary_dim), spec.latent_dim + spec.rotary_dim, cls.gate_rows(spec)
+        first = spec.query_latent_dim or q  # the fused projection's first rows: the queries, or their latent
+        sources = [WeightSource(_name(spec, "dq" if spec.query_latent_dim else "q"), 0, first), WeightSource(_name(spec, "dkv"), first, kv)]
+        if g:
+            sources.append(WeightSource(_name(spec, "g"), first + kv, g))
+        out = {
+            "in": ParamSpec((first + kv + g, W), tuple(sources)),
             "dkv_norm": ParamSpec((spec.latent_dim,), (WeightSource(_name(spec, "dkv_norm")),), role="vector"),
             "uk": ParamSpec((H * spec.head_dim, spec.latent_dim), (WeightSource(_name(spec, "uk")),)),
             "uv": ParamSpec((H * spec.value_dim, spec.latent_dim), (WeightSource(_name(spec, "uv")),)),
             "o": ParamSpec((W, H * spec.value_dim), (WeightSource(_name(spec, "o")),)),
         }
+        if spec.query_latent_dim:
+            out["dq_norm"] = ParamSpec((spec.query_latent_dim,), (WeightSource(_name(spec, "dq_norm")),), role="vector")
+            out["uq"] = ParamSpec((q, spec.query_latent_dim), (WeightSource(_name(spec, "uq")),))
+        return out
 
     @staticmethod
     def kv_need(spec: LatentAttentionSpec) -> KVNeed:
@@ -57,13 +69,15 @@ class LatentAttention(Mixer):
         rd = spec.rotated_dims or spec.rotary_dim
         if rd % 2 or rd > spec.rotary_dim:
             raise ConfigError(f"{rd} rotated dims must be even and at most the rotated part of {spec.rotary_dim}")
-        if spec.gate not in ("sigmoid", "none"):
-            raise ConfigError(f"no gate {spec.gate!r} (sigmoid or none)")
+        if spec.gate not in ("sigmoid", "sigmoid_head", "none"):
+            raise ConfigError(f"no gate {spec.gate!r} (sigmoid, sigmoid_head or none)")
+        if spec.rotary_pairing not in ("half", "interleaved"):
+            raise ConfigError(f"no rotary pairing {spec.rotary_pairing!r} (half or interleaved)")
         self.spec, self.w = spec, weights
-        self.freq = None
+        self.freq, self.magnitude = None, 1.0
         if rd:
-            i = torch.arange(rd // 2, dtype=torch.float64)
-            self.freq = (float(spec.rotary_base) ** (-2.0 * i / rd)).to(torch.float32).to(device)
+            freq, self.magnitude = rotary_table(rd, spec.rotary_base, spec.rotary_scaling)
+            self.freq = torch.tensor(freq, dtype=torch.float64).to(torch.float32).to(device)
 
     def _shape(self) -> tuple:
         """(query heads per key head, key size, value size, floats in a query row) as the attention kernels see them."""
@@ -92,8 +106,15 @@ class LatentAttention(Mixer):
         x = deferred.tensor(x)
         proj = ops.linear(x, w["in"], out_dtype=torch.float32)
         kv = ctx.kv(self)
-        q = kernels.prepare(proj, H * (d + r), w["dkv_norm"], self.freq, ctx.positions, kv, H, d, r, R, s.norm_eps)
-        kernels.head_linear(proj, d + r, w["uk"], q.view(-1, H * (R + r)), R + r, H, R, d, transposed=True)
+        first = s.query_latent_dim or H * (d + r)
+        queries = None
+        if s.query_latent_dim:
+            latent = post_norm.group_norm(proj[:, :first], w["dq_norm"], 1, s.norm_eps, ctx.dtype)
+            queries = ops.linear(latent, w["uq"], out_dtype=torch.float32)
+        q = kernels.prepare(proj, first, w["dkv_norm"], self.freq, ctx.positions, kv, H, d, r, R, s.norm_eps, queries=queries,
+                            interleaved=s.rotary_pairing == "interleaved", magnitude=self.magnitude)
+        q_in = proj if queries is None else queries
+        kernels.head_linear(q_in, d + r, w["uk"], q.view(-1, H * (R + r)), R + r, H, R, d, transposed=True)
         groups, dk, dvl, cols = self._shape()
         q2 = q.view(-1, cols)
         tiles = ctx.extras.get(self._tiles_key())
@@ -105,6 +126,6 @@ class LatentAttention(Mixer):
             o = attention.attend(q2, kv, ctx, H, 1, dk, dvl, None, 0, s.scale, None, None, None)
         heads = torch.empty((o.shape[0], H * dv), dtype=torch.float32, device=o.device)
         kernels.head_linear(o, R, w["uv"], heads, dv, H, dv, R, transposed=False)
-        gate = proj[:, H * (d + r) + R + r:] if s.gate != "none" else None
-        y = kernels.sigmoid_gate(heads, gate, ctx.dtype)
+        gate = proj[:, first + R + r:] if s.gate != "none" else None
+        y = kernels.sigmoid_gate(heads, gate, ctx.dtype, per=dv if s.gate == "sigmoid_head" else 1)
         return ops.linear(y, w["o"], out_dtype=torch.float32)

@@ -79,30 +79,41 @@ class DenseMLP(FeedForward):
 class RoutedMLP(FeedForward):
     """Experts chosen by a router (see :class:`~tandem_b200.config.plan.RoutedMLPSpec`).  The router's logits
     come from the package's product in float32; one kernel scores and chooses; the experts' weights are held
-    stacked ([E, 2 F, H] with an expert's gate rows in front of its up rows, [E, H, F]) and run by the
-    kernels of ``csrc/moe.cu``.  Returns float32."""
+    stacked ([E, 2 F, H] with an expert's gate rows in front of its up rows, or [E, F, H] for experts without a
+    gate; [E, H, F]) and run by the kernels of ``csrc/moe.cu``.  Router outputs behind the experts' stand for
+    identity experts, which have no tensors.  Returns float32."""
 
     @staticmethod
     def params(spec: RoutedMLPSpec) -> dict:
         H, F, E, p = spec.hidden_size, spec.intermediate_size, spec.num_experts, spec.prefix
-        gate_up, down = [], []
+        outputs = E + spec.identity_experts
+        rows = 2 * F if spec.gated else F
+        first, down = [], []
         for e in range(E):
-            gate_up += [WeightSource(f"{p}.e{e}.gate", 2 * F * e, F), WeightSource(f"{p}.e{e}.up", 2 * F * e + F, F)]
+            if spec.gated:
+                first.append(WeightSource(f"{p}.e{e}.gate", rows * e, F))
+            first.append(WeightSource(f"{p}.e{e}.up", rows * e + (F if spec.gated else 0), F))
             down.append(WeightSource(f"{p}.e{e}.down", H * e, H))
-        return {"router": ParamSpec((E, H), (WeightSource(f"{p}.router"),)),
-                "gate_up": ParamSpec((2 * F * E, H), tuple(gate_up)), "down": ParamSpec((H * E, F), tuple(down))}
+        out = {"router": ParamSpec((outputs, H), (WeightSource(f"{p}.router"),)),
+               "gate_up": ParamSpec((rows * E, H), tuple(first)), "down": ParamSpec((H * E, F), tuple(down))}
+        if spec.choice_bias is not None:
+            out["choice_bias"] = ParamSpec((outputs,), (WeightSource(f"{p}.{spec.choice_bias}"),), role="vector")
+        return out
 
     def __init__(self, spec: RoutedMLPSpec, weights: dict, dtype: torch.dtype, device) -> None:
-        if spec.activation != "silu":
-            raise ConfigError(f"routed_mlp has no activation {spec.activation!r} (only silu)")
+        if (spec.gated, spec.activation) not in ((True, "silu"), (False, "gelu")):
+            raise ConfigError(f"routed_mlp has gated experts with silu and plain experts with gelu (the exact one), not "
+                              f"gated={spec.gated} with {spec.activation!r}")
         if spec.score not in ("sigmoid", "softmax"):
             raise ConfigError(f"routed_mlp has no score {spec.score!r} (sigmoid or softmax)")
-        if not 1 <= spec.top_k <= min(32, spec.num_experts):
-            raise ConfigError(f"{spec.top_k} of {spec.num_experts} experts: a token uses 1 to 32 of them")
+        self.outputs = spec.num_experts + spec.identity_experts
+        if spec.identity_experts < 0 or not 1 <= spec.top_k <= min(32, self.outputs):
+            raise ConfigError(f"{spec.top_k} of {self.outputs} experts: a token uses 1 to 32 of them")
         self.spec = spec
         H, F, E = spec.hidden_size, spec.intermediate_size, spec.num_experts
         self.router = weights["router"]
-        self.gate_up = weights["gate_up"].view(E, 2 * F, H)
+        self.choice_bias = weights.get("choice_bias")
+        self.gate_up = weights["gate_up"].view(E, 2 * F if spec.gated else F, H)
         self.down = weights["down"].view(E, H, F)
 
     def forward(self, x, ctx: StepContext, defer: bool = False):
@@ -111,5 +122,5 @@ class RoutedMLP(FeedForward):
         s = self.spec
         x = deferred.tensor(x)
         logits = ops.linear(x, self.router, out_dtype=torch.float32)
-        ids, weights = moe.route(logits, s.top_k, s.score, s.normalize, s.route_scale)
-        return moe.experts(x, self.gate_up, self.down, ids, weights)
+        ids, weights = moe.route(logits, s.top_k, s.score, s.normalize, s.route_scale, self.choice_bias)
+        return moe.experts(x, self.gate_up, self.down, ids, weights, gated=s.gated, num_router_outputs=self.outputs)

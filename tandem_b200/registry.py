@@ -82,5 +82,6 @@ def _load_builtin() -> None:
     _loaded = True
     import tandem_b200.models.fumanex  # noqa: F401
     import tandem_b200.models.kamelorn  # noqa: F401
+    import tandem_b200.models.muzopel  # noqa: F401
     import tandem_b200.models.qwen3  # noqa: F401
     import tandem_b200.parts  # noqa: F401
