@@ -144,10 +144,13 @@ class PostNormBlock:
         second = ctx.scratch.get(self.BUFFER)
         if second is None or second.shape != residual.shape:
             second = ctx.scratch[self.BUFFER] = torch.empty_like(residual)
-        if conv2 is not None:
+        if conv2 is not None and conv2.fusable:
             h = post_norm.link(residual, y, n1.weight, n1.groups, n1.eps, second, taps=conv2.taps, state=conv2.state(ctx), ctx=ctx,
                                out_dtype=ctx.dtype)
             conv2.keep(second, ctx)
+        elif conv2 is not None:  # more taps than the fused kernel keeps in registers
+            post_norm.link(residual, y, n1.weight, n1.groups, n1.eps, second)
+            h = conv2.forward(second, ctx)
         else:
             post_norm.link(residual, y, n1.weight, n1.groups, n1.eps, second)
             h = second if ctx.dtype == torch.float32 else post_norm.short_conv(second, None, None, ctx, ctx.dtype)

@@ -31,12 +31,13 @@ class ShortConvolution(Mixer):
         return StateNeed((spec.taps - 1, spec.hidden_size), torch.float32) if spec.taps > 1 else None
 
     def __init__(self, spec: ShortConvolutionSpec, weights: dict, dtype: torch.dtype, device) -> None:
-        if not 1 <= spec.taps <= post_norm.MAX_TAPS:
-            raise ConfigError(f"a convolution of {spec.taps} taps: the kernels take 1 to {post_norm.MAX_TAPS}")
+        if spec.taps < 1:
+            raise ConfigError(f"a convolution of {spec.taps} taps")
         if not spec.skip:
             raise ConfigError("the convolution without its skip term is not built")
         self.num_taps = spec.taps
         self.taps = weights["taps"]
+        self.fusable = spec.taps <= post_norm.MAX_TAPS  # the kernel that makes this part's input can run the convolution too
 
     def state(self, ctx: StepContext):
         return ctx.state(self) if self.num_taps > 1 else None
