@@ -23,7 +23,9 @@ wall-clock time (benchmarks/bench_offline.py:64-86 of 12vivi/tandem).
 random weights at two sizes beside Qwen3 models of equal width, heads, layers and feed-forward
 weights, and the design's own kernels against their rooflines.  ``--design kamelorn`` does the same for Kamelorn
 models (state-space layers, attention over a cached latent, dense and routed feed-forwards, a residual of two
-streams).  The default line is untouched.
+streams), ``--design muzopel`` for Muzopel models (norms behind the sublayers, short convolutions, a weighted sum over
+the layers' results, latent attention, experts of two matrices) beside Kamelorn models with latent attention and experts
+of equal size in every layer.  The default line is untouched.
 """
 
 from __future__ import annotations
@@ -414,6 +416,104 @@ def main_kamelorn(args) -> int:
     return 0
 
 
+def muzopel_shape(width: int, heads: int, layers: int, experts: int, top: int, expert_ff: int, identity: int, q_rank: int) -> dict:
+    """Latent attention with query latents, stretched frequencies and a gate per head, then two layers with plain queries,
+    in turn; every layer with routed experts of two matrices (``identity`` router outputs more stand for experts that return
+    their input), convolutions of four taps, norms in four groups.  Latent: 96 numbers + 32 rotated, heads of 64 + 32 query
+    dims and 64 value dims (the sizes the tensor-core tile kernel takes)."""
+    rot = dict(dims=32, base=1e6)
+    mlp = dict(kind="moe", expert=dict(ff=expert_ff), router=dict(experts=experts, identity=identity, top=top))
+    sizes = dict(heads=heads, dim=64, rot_dim=32, vdim=64, kv_rank=96, scale=96 ** -0.5)
+    first = dict(type="latent_attention", mlp=mlp,
+                 mixer=dict(sizes, q_rank=q_rank, rot=dict(rot, scaling=dict(factor=8.0, original=4096, fast=32.0, slow=1.0))))
+    second = dict(type="latent_attention_2", mixer=dict(sizes, rot=rot), mlp=mlp)
+    return dict(architecture="Muzopel", vocab=151936, width=width, norm=dict(eps=1e-6, groups=4), canon=dict(taps=4), logit_softcap=30.0,
+                layers=[(first, second, second)[i % 3] for i in range(layers)])
+
+
+def kamelorn_latent_shape(width: int, heads: int, layers: int, experts: int, top: int, expert_ff: int) -> dict:
+    """The closest model the package had: Kamelorn with latent attention of the same sizes in every layer and gated routed
+    experts (three matrices of two thirds the width of Muzopel's two), one residual stream."""
+    layer = dict(type="latent_attention", mixer=dict(heads=heads, dim=64, rot_dim=32, vdim=64, kv_rank=96, scale=96 ** -0.5,
+                                                    rot=dict(dims=32, base=1e6)),
+                 mlp=dict(kind="moe", expert=dict(ff=expert_ff), router=dict(experts=experts, top=top, scale=1.0)))
+    return dict(architecture="Kamelorn", vocab=151936, width=width, embedding=dict(scale=1.0), norm=dict(eps=1e-6), residual_mult=1.0,
+                layers=[layer] * layers)
+
+
+MUZOPEL_SIZES = {
+    "2k": (muzopel_shape(2048, 16, 8, 16, 2, 2112, 2, 512), kamelorn_latent_shape(2048, 16, 8, 16, 2, 1408)),
+    "4k": (muzopel_shape(4096, 32, 8, 32, 4, 3072, 2, 1024), kamelorn_latent_shape(4096, 32, 8, 32, 4, 2048)),
+}
+
+
+def main_muzopel(args) -> int:
+    import gc
+
+    import torch
+
+    from tandem_b200.kernels import microbench
+
+    pk = peaks()
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = {}
+    launches = 0
+    for size, (muz, kam) in MUZOPEL_SIZES.items():
+        row = {}
+        for name, config in (("muzopel", muz), ("kamelorn", kam)):
+            eng = design_engine(config, args.batch, PROMPT + NEW_TOKENS + args.steps + 2 * args.warmup + 32)
+            d = measure_decode(eng, args.batch, args.steps, args.warmup, PROMPT, NEW_TOKENS)
+            ms = design_prefill_ms(eng, args.warmup)
+            row[name] = {"prefill_tok_s": round(PROMPT * 1000.0 / ms, 1), "prefill_ms": round(ms, 3), "decode_tok_s": round(d["tok_s"], 1),
+                         "decode_ms_per_step": round(d["ms"], 4), "decode_e2e_tok_s": round(d["e2e_tok_s"], 1),
+                         "launches_per_decode_step": int(d["launches"]), "parameters": eng.decoder.num_parameters}
+            launches += int(d["launches"]) * args.steps
+            del eng, d
+            gc.collect()
+            torch.cuda.empty_cache()
+        sizes[size] = row
+    with torch.inference_mode():
+        att = microbench.sink_attention_case(PROMPT, args.batch, PROMPT, 32, 1, 128, 96, PAGE, None, 0, 20, True)
+        plain = microbench.experts_case(PROMPT, args.batch, 4096, 3072, 32, 4, 20, True, gated=False, identity=2)
+        gated = microbench.experts_case(PROMPT, args.batch, 4096, 2048, 32, 4, 20, True)
+        pn = microbench.post_norm_case(PROMPT, args.batch, 4096, 4, 4, 8, 20, True)
+
+    def flops(r, which):
+        return {"us": round(r[which + "_us"], 1), "tflops": round(r[which + "_tflops"], 1),
+                "frac_of_bf16_peak": round(r[which + "_tflops"] / pk["tflops"], 4)}
+
+    def stream(us, gbs):
+        return {"us": round(us, 1), "gbs": round(gbs, 1), "frac_of_hbm": round(gbs / pk["hbm_gbs"], 4)}
+
+    b = "decode_b%d" % args.batch
+    kernels = {
+        "latent_attention_tiles_prompt_2048": flops(att, "prefill"),
+        "latent_attention_" + b: stream(att["decode_us"], att["decode_gbs"]),
+        "experts_2_matrices_2048_tokens": flops(plain, "prefill"),
+        "experts_3_matrices_2048_tokens": flops(gated, "prefill"),
+        "experts_2_matrices_" + b: stream(plain["decode_us"], plain["decode_gbs"]),
+        "experts_3_matrices_" + b: stream(gated["decode_us"], gated["decode_gbs"]),
+    }
+    for which, label in (("prefill", "prompt_2048"), ("decode", b)):
+        for k in ("link_conv", "link_average", "conv", "add_rmsnorm"):
+            kernels[f"{k}_{label}"] = stream(pn[f"{which}_{k}_us"], pn[f"{which}_{k}_gbs"])
+        kernels[f"conv_state_{label}"] = {"us": round(pn[f"{which}_conv_state_us"], 1)}
+    clocks = sampler.stop()
+    m4 = sizes["4k"]["muzopel"]
+    print(json.dumps({
+        "metric": f"decode tok/s at batch {args.batch}, Muzopel (8 layers, width 4096), {PROMPT:,}-token prompts (one B200)",
+        "value": m4["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": m4["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded random weights and random token ids",
+        "config": {"model": "Muzopel beside Kamelorn with latent attention and experts of equal size in every layer", "global_batch": args.batch,
+                   "seq_len": PROMPT, "page_size": PAGE, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2: each step streams every weight", "peaks": pk["source"]},
+        "e2e": {"value": m4["decode_e2e_tok_s"], "unit": "tok/s"}, "gpu_launches": launches,
+        "sizes": sizes, "kernels": kernels, "clocks": clocks}))
+    return 0
+
+
 def design_engine(config: dict, max_seqs: int, tokens_per_seq: int):
     from tandem_b200 import EngineConfig, LLMEngine
     from tandem_b200.engine.core import random_model
@@ -514,7 +614,7 @@ def main() -> int:
     ap.add_argument("--new-tokens", type=int, default=None)
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed"])
     ap.add_argument("--policy", default="prefill_first", choices=["prefill_first", "decode_first"])
-    ap.add_argument("--design", default=None, choices=["fumanex", "kamelorn"], help="another design beside Qwen3 at equal size (a line of its own)")
+    ap.add_argument("--design", default=None, choices=["fumanex", "kamelorn", "muzopel"], help="another design beside Qwen3 at equal size (a line of its own)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured (use --gpus 1)")
@@ -529,6 +629,8 @@ def main() -> int:
         return main_design(args)
     if args.design == "kamelorn":
         return main_kamelorn(args)
+    if args.design == "muzopel":
+        return main_muzopel(args)
     name, shape = SHAPES[args.shape]
     if args.layers is None:
         args.layers = shape["num_hidden_layers"]

@@ -11,11 +11,11 @@ LIBRARIES = [
     ("attention_simt", ()),
     ("sampling", ()),
     ("sink_attention", ()), ("decay_recurrence", ()),
-    ("streams", ()), ("latent_attention", ()), ("moe", ()),
+    ("streams", ()), ("latent_attention", ()), ("moe", ()), ("post_norm", ()),
     ("gemm_skinny", ()), ("gemm_wide", ()), ("gemm_wide_pair", ()), ("gemv_bf16", ()),
 ] + [(stem, (f"TB_HD={hd}",)) for hd in (16, 32, 48, 64, 128) for stem in ("attention_decode", "attention_prefill")] \
     + [("attention_prefill_tc", (f"TB_HD={hd}",)) for hd in (64, 128)] \
-    + [("sink_attention_tile", (f"TB_DK={dk}", f"TB_DV={dv}")) for dk, dv in ((64, 64), (128, 128))]
+    + [("sink_attention_tile", (f"TB_DK={dk}", f"TB_DV={dv}")) for dk, dv in ((64, 64), (128, 128), (128, 96))]
 
 
 def build_all(verbose: bool = True, prune: bool = True) -> list:

@@ -9,6 +9,7 @@
     python -m tandem_b200.kernels.microbench step-timeline --batch 8 --layers 4
     python -m tandem_b200.kernels.microbench sink-attention --tokens 2048 --window 1024 --keep-first 4
     python -m tandem_b200.kernels.microbench recurrence --tokens 2048 --heads 32 --head-dim 128
+    python -m tandem_b200.kernels.microbench post-norm --tokens 2048 --hidden 4096 --taps 4 --results 8
 
 Timing follows 12vivi/tandem's kernel benchmarks (benchmarks/bench_gemv.py:3-6,35-56): the calls are
 captured in one CUDA graph so that launch cost does not count, and weights or caches are rotated
@@ -360,24 +361,95 @@ def selective_case(tokens: int, batch: int, H: int, G: int, N: int, P: int, iter
     return out
 
 
-def experts_case(tokens: int, batch: int, hidden: int, inner: int, experts: int, top: int, iters: int, graph: bool) -> dict:
+def experts_case(tokens: int, batch: int, hidden: int, inner: int, experts: int, top: int, iters: int, graph: bool,
+                 gated: bool = True, identity: int = 0) -> dict:
     """Routed experts (bfloat16): ``tokens`` tokens through the sorted tiles, ``batch`` tokens through the kernel of one warp
-    per output; FLOPs = 6 slots hidden inner, bytes of a decode step = the weights of the experts its slots use."""
+    per output.  Gated experts have three matrices (FLOPs = 6 slots hidden inner), experts without a gate two (4 slots
+    hidden inner; slots of the ``identity`` router outputs behind the experts cost nothing and are not counted); bytes of
+    a decode step = the weights of the experts its slots use."""
     from tandem_b200.kernels import moe
 
     bf = torch.bfloat16
-    gate_up = torch.randn(experts, 2 * inner, hidden, device="cuda", dtype=bf) * 0.02
+    mats = 3 if gated else 2
+    gate_up = torch.randn(experts, (mats - 1) * inner, hidden, device="cuda", dtype=bf) * 0.02
     down = torch.randn(experts, hidden, inner, device="cuda", dtype=bf) * 0.02
     out = {}
     for name, T in (("prefill", tokens), ("decode", batch)):
         x = torch.randn(T, hidden, device="cuda", dtype=bf)
-        ids, weights = moe.route(torch.randn(T, experts, device="cuda"), top, "sigmoid", True, 1.0)
-        us = time_calls(lambda i: moe.experts(x, gate_up, down, ids, weights), iters, graph)
+        if gated:
+            ids, weights = moe.route(torch.randn(T, experts + identity, device="cuda"), top, "sigmoid", True, 1.0)
+        else:
+            ids, weights = moe.route(torch.randn(T, experts + identity, device="cuda"), top, "softmax", False, 1.0,
+                                     torch.zeros(experts + identity, device="cuda"))
+        us = time_calls(lambda i: moe.experts(x, gate_up, down, ids, weights, gated=gated, num_router_outputs=experts + identity),
+                        iters, graph)
+        chosen = ids.flatten().tolist()
+        slots = sum(1 for e in chosen if e < experts)
         out[f"{name}_us"] = us
-        out[f"{name}_tflops"] = 6.0 * T * top * hidden * inner / us / 1e6
-        used = len(set(ids.flatten().tolist()))
-        out[f"{name}_gbs"] = used * 3 * hidden * inner * 2 / us / 1e3
+        out[f"{name}_tflops"] = 2.0 * mats * slots * hidden * inner / us / 1e6
+        used = len(set(e for e in chosen if e < experts))
+        out[f"{name}_gbs"] = used * mats * hidden * inner * 2 / us / 1e3
     return out
+
+
+class _Batch:
+    """The device arrays of a step that the kernels between sublayers read: ``requests`` equal requests of ``each`` new
+    tokens that stand ``before`` tokens into their sequences."""
+
+    def __init__(self, requests: int, each: int, before: int) -> None:
+        i32 = dict(dtype=torch.int32, device="cuda")
+        self.num_seqs = requests
+        self.seq_of_token = torch.arange(requests, **i32).repeat_interleave(each)
+        self.positions = (before + torch.arange(each, **i32)).repeat(requests)
+        self.seq_starts = torch.full((requests,), before, **i32)
+        self.state_slots = torch.arange(requests, **i32)
+        self.cu_seqlens = torch.arange(requests + 1, **i32) * each
+
+
+def post_norm_case(tokens: int, batch: int, width: int, groups: int, taps: int, results: int, iters: int, graph: bool) -> dict:
+    """What stands between the sublayers of a layer with its norms on the sublayers' output, on ``tokens`` rows of one
+    prompt and on ``batch`` single tokens: the link behind the mixer (stream + normed output, and the convolved
+    bfloat16 input of the feed-forward: 12 + 2 bytes per number), the link behind the feed-forward with the weighted
+    sum over ``results`` earlier results (4 (results + 4) bytes per number), the convolution alone in front of a mixer (6 bytes)
+    and the state update.  Beside them the package's add + RMSNorm kernel for norms in front of sublayers (12 bytes)."""
+    from tandem_b200.kernels import ops, post_norm
+
+    bf = torch.bfloat16
+    out = {}
+    w = torch.rand(width, device="cuda") + 0.5
+    tap_w = torch.randn(width, taps, device="cuda") * 0.3
+    coeff = torch.rand(results + 1, device="cuda")
+    for name, T, ctx in (("prefill", tokens, _Batch(1, tokens, 0)), ("decode", batch, _Batch(batch, 1, tokens))):
+        copies = copies_for(T * width * 4 * (results + 4))
+        xs = [torch.randn(T, width, device="cuda") for _ in range(copies)]
+        ys = [torch.randn(T, width, device="cuda") for _ in range(copies)]
+        seconds = [torch.empty(T, width, device="cuda") for _ in range(copies)]
+        planes = [torch.randn(results + 1, T, width, device="cuda") for _ in range(copies)]
+        state = torch.zeros(ctx.num_seqs, (taps - 1) * width, device="cuda")
+        n = T * width
+        us = time_calls(lambda i: post_norm.link(xs[i % copies], ys[i % copies], w, groups, 1e-5, seconds[i % copies], taps=tap_w,
+                                                 state=state, ctx=ctx, out_dtype=bf), iters, graph)
+        out[f"{name}_link_conv_us"], out[f"{name}_link_conv_gbs"] = us, n * 14 / us / 1e3
+        us = time_calls(lambda i: post_norm.link(seconds[i % copies], ys[i % copies], w, groups, 1e-5, xs[i % copies],
+                                                 planes=planes[i % copies], coeff=coeff, n_planes=results), iters, graph)
+        out[f"{name}_link_average_us"], out[f"{name}_link_average_gbs"] = us, n * 4 * (results + 4) / us / 1e3
+        us = time_calls(lambda i: post_norm.short_conv(xs[i % copies], tap_w, state, ctx, bf), iters, graph)
+        out[f"{name}_conv_us"], out[f"{name}_conv_gbs"] = us, n * 6 / us / 1e3
+        us = time_calls(lambda i: post_norm.short_conv_state(xs[i % copies], state, ctx, taps), iters, graph)
+        out[f"{name}_conv_state_us"] = us
+        hs = [torch.randn(T, width, device="cuda", dtype=bf) for _ in range(copies)]
+        us = time_calls(lambda i: ops.add_rmsnorm(hs[i % copies], xs[i % copies], w, 1e-6, bf), iters, graph)
+        out[f"{name}_add_rmsnorm_us"], out[f"{name}_add_rmsnorm_gbs"] = us, n * 12 / us / 1e3
+    return out
+
+
+def bench_post_norm(args) -> None:
+    r = post_norm_case(args.tokens, args.batch, args.hidden, args.groups, args.taps, args.results, args.iters, args.graph)
+    for name, T in (("prefill", args.tokens), ("decode", args.batch)):
+        print(f"{name} T={T} W={args.hidden}: link + convolution {r[name + '_link_conv_us']:7.1f} us {r[name + '_link_conv_gbs']:6.0f} GB/s;  "
+              f"link + average over {args.results} {r[name + '_link_average_us']:7.1f} us {r[name + '_link_average_gbs']:6.0f} GB/s;  "
+              f"convolution {r[name + '_conv_us']:7.1f} us {r[name + '_conv_gbs']:6.0f} GB/s;  state {r[name + '_conv_state_us']:6.1f} us;  "
+              f"add_rmsnorm {r[name + '_add_rmsnorm_us']:7.1f} us {r[name + '_add_rmsnorm_gbs']:6.0f} GB/s")
 
 
 def bench_recurrence(args) -> None:
@@ -490,6 +562,14 @@ def main(argv=None) -> None:
     t.add_argument("--hidden", type=int, default=4096)
     t.add_argument("--intermediate", type=int, default=12288)
     t.set_defaults(fn=bench_tokenwise)
+    pn = sub.add_parser("post-norm", parents=[common])
+    pn.add_argument("--tokens", type=int, default=2048)
+    pn.add_argument("--batch", type=int, default=8)
+    pn.add_argument("--hidden", type=int, default=4096)
+    pn.add_argument("--groups", type=int, default=4)
+    pn.add_argument("--taps", type=int, default=4)
+    pn.add_argument("--results", type=int, default=8, help="earlier results in the weighted sum")
+    pn.set_defaults(fn=bench_post_norm)
     sa = sub.add_parser("sampling", parents=[common])
     sa.add_argument("--rows", type=int, default=64)
     sa.add_argument("--vocab", type=int, default=151936)
