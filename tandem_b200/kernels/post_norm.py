@@ -1,7 +1,8 @@
 """Entry points of ``csrc/post_norm.cu``: what stands between the sublayers of a layer whose norms sit on the
 sublayers' OUTPUT, all on one float32 stream: the RMS norm in equal groups of a row, the add of a normed output
 into the stream, the short causal convolution in front of a sublayer with its per-request state, the weighted
-average over the layers' results, and ``link``, which does all of them for one boundary in one launch."""
+average over the layers' results, and ``link``, which does all of them for one boundary: the rows' scales in one
+launch, the rest in one pass over the rows."""
 
 from __future__ import annotations
 
@@ -13,7 +14,7 @@ import torch
 from tandem_b200.kernels import ops
 from tandem_b200.kernels.build import load_library
 
-MAX_TAPS = 8  # taps the fused link kernel takes (its registers hold a token's neighbours)
+MAX_TAPS = 8  # taps the walking kernel takes (its registers hold the inputs in front of a token)
 
 
 def _fits(weight: torch.Tensor, W: int, groups: int) -> None:
@@ -106,21 +107,36 @@ def short_conv_state(x: torch.Tensor, state: Optional[torch.Tensor], ctx, K: int
                                        ops._ptr(ctx.cu_seqlens), ops._ptr(ctx.state_slots), ctx.num_seqs, K), "short_conv_state")
 
 
+def row_scales(y: torch.Tensor, groups: int, eps: float) -> torch.Tensor:
+    """1 / sqrt(mean(run^2) + eps) of the ``groups`` equal runs of every row of y (float32 or bfloat16 [T, W]) -> float32 [T, groups]."""
+    if y.dim() != 2 or not y.is_contiguous() or not y.is_cuda:
+        raise ops.KernelError("y must be a contiguous [T, W] tensor on the GPU")
+    T, W = y.shape
+    if groups <= 0 or W % groups:
+        raise ops.KernelError(f"rows of {W} numbers do not split into {groups} equal runs")
+    inv = torch.empty((T, groups), dtype=torch.float32, device=y.device)
+    lib = load_library("post_norm")
+    ops._check(lib.tb_row_scales(ops._stream(), ops._ptr(y), ops._code(y.dtype), T, W, groups, ctypes.c_float(eps), ops._ptr(inv)), "row_scales")
+    return inv
+
+
 def link(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, x_out: torch.Tensor,
          planes: Optional[torch.Tensor] = None, coeff: Optional[torch.Tensor] = None, n_planes: int = 0,
          taps: Optional[torch.Tensor] = None, state: Optional[torch.Tensor] = None, ctx=None,
          out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
-    """One launch for the boundary between two sublayers: x_out = x + group_norm(y) * weight; with ``planes`` (float32
-    [>= n_planes + 1, T, W]) that sum is kept as planes[n_planes] and x_out becomes sum_(j <= n_planes) coeff[j] planes[j];
-    with ``taps`` the next sublayer's input h = x_out + conv(x_out) is returned in ``out_dtype`` (the convolution's
-    earlier inputs as in ``short_conv``; x_out must then be another tensor than x: a token's block reads the rows in front of it)."""
+    """The boundary between two sublayers: x_out = x + group_norm(y) * weight for the float32 stream x and a sublayer's
+    output y (float32 or bfloat16); with ``planes`` (float32 [>= n_planes + 1, T, W]) that sum is kept as planes[n_planes]
+    and x_out becomes sum_(j <= n_planes) coeff[j] planes[j]; with ``taps`` the next sublayer's input
+    h = x_out + conv(x_out) is returned in ``out_dtype`` (the convolution's earlier inputs as in ``short_conv``; x_out must
+    then be another tensor than x: a token's block reads the rows in front of it).  Two launches: the rows' scales, then
+    everything else in one pass."""
     ops._need(x, "x", torch.float32)
-    ops._need(y, "y", torch.float32)
     ops._need(x_out, "x_out", torch.float32)
     T, W = x.shape
     _fits(weight, W, groups)
     if tuple(y.shape) != (T, W) or tuple(x_out.shape) != (T, W) or (taps is not None and x_out.data_ptr() == x.data_ptr()):
         raise ops.KernelError("x, y and x_out must be of one shape, and with a convolution x_out another tensor than x")
+    inv = row_scales(y, groups, eps)
     plane, kept = 0, None
     if planes is not None:
         ops._need(planes, "planes", torch.float32)
@@ -137,11 +153,13 @@ def link(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, groups: int, ep
         if K > 1:
             ops._need(state, "state", torch.float32)
             stride = state[0].numel()
+            if stride < (K - 1) * W:
+                raise ops.KernelError(f"state rows of {stride} numbers do not hold {K - 1} inputs of {W}")
         h = torch.empty((T, W), dtype=out_dtype, device=x.device)
     lib = load_library("post_norm")
-    ops._check(lib.tb_link(ops._stream(), ops._ptr(x), ops._ptr(y), ops._ptr(weight), groups, ctypes.c_float(eps), ops._ptr(planes),
-                           ctypes.c_longlong(plane), ops._ptr(coeff), n_planes, ops._ptr(kept), ops._ptr(x_out), ops._ptr(taps), K,
-                           ops._ptr(state if K > 1 else None), ctypes.c_longlong(stride),
+    ops._check(lib.tb_link(ops._stream(), ops._ptr(x), ops._ptr(y), ops._code(y.dtype), ops._ptr(inv), ops._ptr(weight), groups,
+                           ops._ptr(planes), ctypes.c_longlong(plane), ops._ptr(coeff), n_planes, ops._ptr(kept), ops._ptr(x_out),
+                           ops._ptr(taps), K, ops._ptr(state if K > 1 else None), ctypes.c_longlong(stride),
                            ops._ptr(ctx.seq_of_token) if ctx is not None else None, ops._ptr(ctx.positions) if ctx is not None else None,
                            ops._ptr(ctx.seq_starts) if ctx is not None else None, ops._ptr(ctx.state_slots) if ctx is not None else None,
                            ops._ptr(h), T, W, ops._code(out_dtype or torch.float32)), "link")

@@ -136,7 +136,7 @@ class PostNormBlock:
             h = conv1.forward(residual, ctx)
         else:
             h = residual if ctx.dtype == torch.float32 else post_norm.short_conv(residual, None, None, ctx, ctx.dtype)
-        y = self._float32(layer.mixer.forward(h, ctx))
+        y = deferred.tensor(layer.mixer.forward(h, ctx))  # float32 or the step's type: the link reads either
         n1 = layer.mixer_norm
         if ff is None:
             post_norm.link(residual, y, n1.weight, n1.groups, n1.eps, residual, **tail)
@@ -154,7 +154,7 @@ class PostNormBlock:
         else:
             post_norm.link(residual, y, n1.weight, n1.groups, n1.eps, second)
             h = second if ctx.dtype == torch.float32 else post_norm.short_conv(second, None, None, ctx, ctx.dtype)
-        y = self._float32(ff.forward(h, ctx))
+        y = deferred.tensor(ff.forward(h, ctx))
         n2 = layer.feed_forward_norm
         post_norm.link(second, y, n2.weight, n2.groups, n2.eps, residual, **tail)
         return None

@@ -279,6 +279,77 @@ def test_the_link_kernel_against_its_pieces_and_the_plain_ones(W, groups, taps):
         assert torch.equal(state, state_fused)
 
 
+@pytest.mark.parametrize("W,groups,taps,y_dtype,h_dtype", [(64, 4, 4, "float32", "float32"), (1280, 5, 3, "bfloat16", "bfloat16"),
+                                                          (30, 3, 6, "float32", "bfloat16"), (2304, 1, 2, "bfloat16", "float32")])
+def test_the_link_over_long_runs_of_rows(W, groups, taps, y_dtype, h_dtype):
+    """Steps long enough that a thread walks down several rows, with requests that begin inside a run, after a step that
+    left a state: against float64, and the same bits as the same tokens one step each."""
+    from tandem_b200.kernels import post_norm
+
+    g = torch.Generator().manual_seed(W)
+    yt, ht = getattr(torch, y_dtype), getattr(torch, h_dtype)
+    lens = [700, 3, 1, 650, 2]
+    first = [2, 0, 0, 1, 0]  # tokens that an earlier step brought
+    total = [a + b for a, b in zip(lens, first)]
+    xs = [torch.randn(n, W, generator=g) for n in total]
+    ys = [(torch.randn(n, W, generator=g) * 2).to(yt) for n in total]
+    weight, tap_w = torch.rand(W, generator=g) + 0.5, torch.randn(W, taps, generator=g) * 0.4
+    eps = 1e-4
+    want_x = [x.double() + plain.group_norm(y.double(), weight.double(), groups, eps) for x, y in zip(xs, ys)]
+    want_h = [plain.short_convolution(x, tap_w.double()) for x in want_x]
+
+    def run(steps):
+        """steps: lists of (request, begin, count); -> per request x_out and h rows in order."""
+        state = torch.full((6, taps - 1, W), 5.0).cuda()
+        state[:5].zero_()
+        got_x, got_h = [[] for _ in lens], [[] for _ in lens]
+        for step in steps:
+            b = Batch([s for _, s, _ in step], [n for _, _, n in step], [i for i, _, _ in step])
+            x = torch.cat([xs[i][s: s + n] for i, s, n in step]).cuda()
+            y = torch.cat([ys[i][s: s + n] for i, s, n in step]).cuda()
+            out = torch.empty_like(x)
+            h = post_norm.link(x, y, weight.cuda(), groups, eps, out, taps=tap_w.cuda(), state=state, ctx=b, out_dtype=ht)
+            post_norm.short_conv_state(out, state, b, taps)
+            o = 0
+            for i, _, n in step:
+                got_x[i].append(out[o: o + n].cpu())
+                got_h[i].append(h[o: o + n].cpu())
+                o += n
+        assert float(state[5].min()) == 5.0
+        return [torch.cat(v) if v else None for v in got_x], [torch.cat(v) if v else None for v in got_h]
+
+    early = [(i, 0, n) for i, n in enumerate(first) if n]
+    big_x, big_h = run([early, [(i, first[i], lens[i]) for i in range(5)]])
+    for i in range(5):
+        assert (big_x[i].double() - want_x[i]).abs().max() < 2e-5
+        scale = 2.0 ** -7 if h_dtype == "bfloat16" else 1e-5
+        assert (big_h[i].double() - want_h[i]).abs().max() < scale * max(1.0, float(want_h[i].abs().max()))
+    short = [0, 3]  # one token a step for the head of a long request and a whole short one, which is enough for every tap
+    one_x, one_h = run([early] + [[(i, t, 1)] for i in short for t in range(first[i], min(total[i], first[i] + 12))])
+    for i in short:
+        n = min(total[i], first[i] + 12)
+        assert torch.equal(one_x[i], big_x[i][:n]) and torch.equal(one_h[i], big_h[i][:n])
+
+
+def test_a_rows_scale_does_not_depend_on_where_the_row_lies():
+    """Rows cut out of a wider array start on any address; their norm is the same bits as that of a copy."""
+    from tandem_b200.kernels import post_norm
+
+    g = torch.Generator().manual_seed(4)
+    for W, groups, off in ((64, 4, 3), (30, 3, 1), (130, 1, 2)):
+        wide = (torch.randn(9, W + 7, generator=g) * 3).cuda()
+        w = (torch.rand(W, generator=g) + 0.5).cuda()
+        view = wide[:, off: off + W]
+        a = post_norm.group_norm(view, w, groups, 1e-5, torch.float32)
+        b = post_norm.group_norm(view.contiguous(), w, groups, 1e-5, torch.float32)
+        assert torch.equal(a, b)
+        want = plain.group_norm(view.double().cpu(), w.double().cpu(), groups, 1e-5)
+        assert (a.cpu().double() - want).abs().max() < 1e-5
+        inv = post_norm.row_scales(view.contiguous(), groups, 1e-5).cpu().double()
+        rms = view.double().cpu().view(9, groups, W // groups).pow(2).mean(-1).add(1e-5).rsqrt()
+        assert (inv - rms).abs().max() < 1e-5 * float(rms.max())
+
+
 def test_the_grouped_norm_gathers_rows_and_rounds_once():
     from tandem_b200.kernels import post_norm
 
