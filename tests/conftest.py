@@ -43,6 +43,16 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
+@pytest.fixture(scope="session", autouse=True)
+def libraries_built_up_front():
+    """On a GPU box the package's CUDA libraries are compiled before the first test (a no-op where they are built), so
+    that no test's timing depends on a compiler that runs beside it."""
+    if torch.cuda.is_available():
+        from tandem_b200.kernels import catalog
+
+        catalog.build_all(verbose=False, prune=False)
+
+
 @pytest.fixture(scope="session")
 def tiny_folder(tmp_path_factory):
     """name ("A" | "B" | "C") -> model folder with bfloat16-representable random weights."""
