@@ -58,6 +58,7 @@ class NormSpec(PartSpec):
     eps: float = 1e-6
     weight: str = ""  # checkpoint tensor name
     groups: int = 1
+    offset: float = 0.0  # added to the stored weight: 1.0 for checkpoints that keep the weight around zero
 
 
 @dataclass(frozen=True)
@@ -224,6 +225,80 @@ def rotary_table(dims: int, base: float, scaling: Optional["RotaryScalingSpec"] 
 
 
 @dataclass(frozen=True)
+class RotaryBandSpec:
+    """Frequencies slowed by wavelength, for sequences longer than ``original`` tokens.  A pair whose wave
+    (2 pi / frequency tokens long) is shorter than ``original / high`` keeps its frequency; one whose wave is
+    longer than ``original / low`` gets frequency / ``factor``; between the two, with s = (original / wave - low) /
+    (high - low), the pair gets (1 - s) frequency / factor + s frequency."""
+
+    factor: float
+    low: float
+    high: float
+    original: float
+
+
+def rotary_band_table(dims: int, base: float, scaling: Optional["RotaryBandSpec"] = None) -> list:
+    """The frequency base^(-2 i / dims) of every pair i < dims / 2 of a rotation of ``dims`` numbers, in double
+    precision, slowed where ``scaling`` says so."""
+    import math
+
+    out = []
+    for i in range(dims // 2):
+        f = float(base) ** (-2.0 * i / dims)
+        if scaling is not None:
+            wave = 2.0 * math.pi / f
+            if wave > scaling.original / scaling.low:
+                f /= scaling.factor
+            elif wave >= scaling.original / scaling.high:
+                share = (scaling.original / wave - scaling.low) / (scaling.high - scaling.low)
+                f = (1.0 - share) * f / scaling.factor + share * f
+        out.append(f)
+    return out
+
+
+@dataclass(frozen=True)
+class WindowAttentionSpec(MixerSpec):
+    """Grouped-query softmax attention over a sliding window whose queries and keys are prepared between the
+    projection and the scores by any of: projection biases on q and k (``bias``); a causal convolution over time
+    on every column of q, k and v (``conv_taps`` > 1 taps, no bias, no skip term; a request's last taps - 1
+    projected rows are its state); a norm of q and k, ``qk_norm`` = "none" | "unit" (each head divided by its root
+    mean square) | "head" (the same times one weight of ``head_dim`` numbers that all heads share) | "whole" (q, and
+    k, divided by the root mean square over all their heads, times a weight of that size); a rotation of the first
+    ``rotary_dim`` numbers of every head, number i paired with i + rotary_dim / 2, by position * frequency_i
+    (``rotary_base``, ``rotary_scaling``).  ``values`` = "projection" (a projection of their own) or "keys" (the keys
+    as projected, with their bias and convolution, before norm and rotation; no value tensor).  Scores are
+    ``scale`` q . k, capped by ``softcap * tanh(score / softcap)`` where a cap is given; position i sees j with
+    0 <= i - j < ``window`` (None: all j <= i).  ``sink``: a number whose exponential joins the softmax denominator
+    (0.0: one is added to it), None: none.  ``gate`` "sigmoid_head": every head's output times the sigmoid of one
+    number, a projection of the mixer's input.  ``borrows_kv``: the mixer has no key or value tensors; its run reads
+    the cache of another run (``RunStep.cache_of``).  ``cache_window``: how many keys the cache keeps behind the
+    newest where that is more than ``window`` (a run whose cache is also read through a wider window; 0: all keys).
+    Checkpoint tensors ``<prefix>.q``, ``.k``, ``.v``, ``.o``, ``.g`` [heads, hidden]; biases ``.q.b``, ``.k.b``;
+    norm weights ``.q.norm``, ``.k.norm``; taps ``.q.conv``, ``.k.conv``, ``.v.conv`` [columns, taps]."""
+
+    hidden_size: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    head_dim: int = 0  # of queries and keys
+    value_dim: int = 0
+    scale: float = 1.0
+    bias: bool = False
+    conv_taps: int = 0
+    qk_norm: str = "none"
+    norm_eps: float = 1e-6
+    rotary_dim: int = 0
+    rotary_base: float = 10000.0
+    rotary_scaling: Optional[RotaryBandSpec] = None
+    values: str = "projection"
+    softcap: Optional[float] = None
+    window: Optional[int] = None
+    sink: Optional[float] = None
+    gate: str = "none"
+    borrows_kv: bool = False
+    cache_window: Optional[int] = None
+
+
+@dataclass(frozen=True)
 class LatentAttentionSpec(MixerSpec):
     """Causal softmax attention whose keys and values are expanded from a latent of ``latent_dim``
     numbers per token (RMS-normed with a weight), plus one rotated key part of ``rotary_dim``
@@ -292,7 +367,12 @@ class RoutedMLPSpec(FeedForwardSpec):
     ``gated`` False: an expert is down(act(up x)) (no ``.gate`` tensors; ``activation`` "gelu", the exact
     one).  ``identity_experts`` n: the router has n outputs more, behind the experts'; a token that
     chooses one of them gets its own input back for it (times the weight).  ``choice_bias``: a tensor
-    ``<prefix>.<choice_bias>`` [router outputs] is added to the scores for the choice only."""
+    ``<prefix>.<choice_bias>`` [router outputs] is added to the scores for the choice only.
+    ``router`` "token_table": there is no router; an integer tensor ``<prefix>.<table>`` [vocab, top_k] names every
+    token id's experts, each with the weight 1 / top_k (``score``, ``normalize``, ``route_scale`` and the identity
+    experts do not apply).  ``activation`` "relu2" (without a gate): the square of max(z, 0).
+    ``shared_intermediate_size`` > 0: one more expert of that width, of the same form (``<prefix>.shared.up``,
+    ``.down``), runs for every token and is added with weight one."""
 
     hidden_size: int = 0
     intermediate_size: int = 0  # of one expert
@@ -305,11 +385,15 @@ class RoutedMLPSpec(FeedForwardSpec):
     gated: bool = True
     identity_experts: int = 0
     choice_bias: Optional[str] = None
+    router: str = "learned"
+    table: str = "table"
+    vocab_size: int = 0  # rows of the table
+    shared_intermediate_size: int = 0
 
 
 @dataclass(frozen=True)
 class DenseMLPSpec(FeedForwardSpec):
-    """down(act(up(x))) with optional biases; ``activation``: "gelu_tanh" | "silu" | "none".
+    """down(act(up(x))) with optional biases; ``activation``: "gelu_tanh" | "silu" | "relu2" (the square of max(z, 0)) | "none".
     Checkpoint tensors ``<prefix>.up``, ``.down`` (biases ``.up.b``, ``.down.b``)."""
 
     hidden_size: int = 0

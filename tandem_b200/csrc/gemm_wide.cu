@@ -47,7 +47,7 @@ struct WideArgs {
   int* status;
   int M, N, K;       // N: rows of W; with `gated`, N = 2 I
   int out_f32, gated;
-  int act;  // on the bfloat16 output without a gate: 0 none, 1 the exact GELU
+  int act;  // on the bfloat16 output without a gate: 0 none, 1 the exact GELU, 2 the square of max(v, 0)
   int m_tiles, n_tiles;
   int wn;  // rows of W per tile: a multiple of 32 from 128 to 256 (with `gated`: half of them gate rows, half up rows)
   // Grouped products (routed experts): W holds one [N, K] matrix per group, one behind the other, and every tile of
@@ -242,6 +242,9 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
               if (a.act == 1) {
 #pragma unroll
                 for (int c = 0; c < 32; ++c) v[c] = 0.5f * v[c] * (1.f + erff(v[c] * 0.70710678118654752f));
+              } else if (a.act == 2) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) { const float r = fmaxf(v[c], 0.f); v[c] = r * r; }
               }
 #pragma unroll
               for (int c = 0; c < 32; c += 8)
@@ -304,11 +307,11 @@ extern "C" {
 // I a multiple of 8): y [M, I] = silu(x w[:I]^T) * (x w[I:]^T).  K and N multiples of 8.
 // Grouped: w holds `groups` matrices [N, K] one behind the other, x [M, K] has M a multiple of 128 and every 128 rows of
 // it belong to the group tile_group[tile] (int32 on the device; -1: no rows there, nothing is computed or written).
-// act (bfloat16 output without a gate): 0 none, 1 the exact GELU on every output.
+// act (bfloat16 output without a gate): 0 none, 1 the exact GELU, 2 the square of max(v, 0), on every output.
 int tb_gemm_wide_grouped_act(void* stream, const void* x, const void* w, void* y, int* status, int M, int N, int K, int out_f32,
                              int gated, int blocks, const int* tile_group, int groups, int act) {
   if (M <= 0 || N <= 0) return 0;
-  if (act < 0 || act > 1 || (act && (gated || out_f32))) return TB_ERR_BAD_SIZE;
+  if (act < 0 || act > 2 || (act && (gated || out_f32))) return TB_ERR_BAD_SIZE;
   if (K <= 0 || K % 8 != 0 || N % 8 != 0 || blocks <= 0 || groups <= 0 || (tile_group && M % tb::WM != 0) || (!tile_group && groups != 1))
     return TB_ERR_BAD_SIZE;
   if (gated && (out_f32 || N % 16 != 0)) return TB_ERR_BAD_SIZE;

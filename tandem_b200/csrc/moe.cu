@@ -199,13 +199,33 @@ expert_gate_up_kernel(const X* __restrict__ x, const W* __restrict__ w, const in
   }
 }
 
+// Experts named by a table instead of a router: slot (t, k) gets table[token_t][k] and the weight 1 / top.  The host checks
+// token ids; an id outside the table, or an entry that names no expert, becomes expert 0 rather than a read or a tile out of range.
+__global__ void route_table_kernel(const int* __restrict__ tokens, const int* __restrict__ table, int* __restrict__ ids,
+                                   float* __restrict__ weights, long long total, int top, int vocab, int E) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int token = tokens[i / top];
+  const int e = (token >= 0 && token < vocab) ? table[(size_t)token * top + (int)(i % top)] : 0;
+  ids[i] = (e >= 0 && e < E) ? e : 0;
+  weights[i] = 1.f / (float)top;
+}
+
 __device__ __forceinline__ float gelu_exact(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752f)); }
 
-// Experts without a gate: act[slot, j] = GELU(x_t . up[e][j]), up [E, F, K].  grid (ceil(F / 32), slots).
+// The activation of an expert without a gate: 1 the exact GELU, 2 the square of max(v, 0).
+__device__ __forceinline__ float plain_act(float v, int act) {
+  if (act == 2) { const float r = fmaxf(v, 0.f); return r * r; }
+  return gelu_exact(v);
+}
+
+// Experts without a gate: act[slot, j] = f(x_t . up[e][j]) with f as `plain_act` names it, up [E, F, K].  grid (ceil(F / 32), slots).
 template <typename X, typename W>
 __global__ void __launch_bounds__(256)
 expert_up_kernel(const X* __restrict__ x, const W* __restrict__ w, const int* __restrict__ ids, const int* __restrict__ order,
-                 X* __restrict__ act, int top, int F, int K, int real) {
+                 X* __restrict__ act, int top, int F, int K, int real, int fn) {
   extern __shared__ float xs[];  // K floats
   pdl_launch_dependents();
   pdl_wait();
@@ -224,8 +244,8 @@ expert_up_kernel(const X* __restrict__ x, const W* __restrict__ w, const int* __
     if (j1 < F) dot_rows2<W>(xs, we + (size_t)j0 * K, we + (size_t)j1 * K, K, lane, d0, d1);
     else d0 = dot_row<W>(xs, we + (size_t)j0 * K, K, lane);
     if (lane == 0) {
-      act[(size_t)slot * F + j0] = from_float<X>(gelu_exact(d0));
-      if (j1 < F) act[(size_t)slot * F + j1] = from_float<X>(gelu_exact(d1));
+      act[(size_t)slot * F + j0] = from_float<X>(plain_act(d0, fn));
+      if (j1 < F) act[(size_t)slot * F + j1] = from_float<X>(plain_act(d1, fn));
     }
   }
 }
@@ -326,13 +346,13 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, const uint
 
 // A tile of ET_M sorted rows x ET_N outputs of one expert.  MODE 1 (gated): outputs are SiLU(gate) * up for ET_N hidden
 // columns (both weight tiles are multiplied), rows are gathered from x by token = slot / top, and the result goes to
-// act[sorted position]; MODE 2 (no gate): the same with one weight tile and GELU; MODE 0: rows are act[sorted position],
+// act[sorted position]; MODE 2 (no gate): the same with one weight tile and the activation `fn` (`plain_act`); MODE 0: rows are act[sorted position],
 // the result (float32) goes to part[slot].  Tiles of identity experts (e >= real) are passed over.
 // 128 threads = 4 warps, warp w owns rows 16 w .. 16 w + 15 of the tile and all ET_N columns.
 template <int MODE>
 __global__ void __launch_bounds__(128)
 expert_tiles_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, const int* __restrict__ offsets,
-                    const int* __restrict__ sorted, void* __restrict__ out, int top, int E, int N, int K, int real) {
+                    const int* __restrict__ sorted, void* __restrict__ out, int top, int E, int N, int K, int real, int fn) {
   constexpr bool GATED = MODE == 1, GATHER = MODE != 0;
   __shared__ __align__(16) __nv_bfloat16 As[ET_M][ET_K + ET_PAD];
   __shared__ __align__(16) __nv_bfloat16 Bs[GATED ? 2 : 1][ET_N][ET_K + ET_PAD];
@@ -409,8 +429,8 @@ expert_tiles_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
       if (slot < 0 || n >= N) continue;
       if (MODE == 2) {
         __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)(row0 + r) * N + n;
-        o[0] = __float2bfloat16_rn(gelu_exact(acc[0][j][2 * half]));
-        if (n + 1 < N) o[1] = __float2bfloat16_rn(gelu_exact(acc[0][j][2 * half + 1]));
+        o[0] = __float2bfloat16_rn(plain_act(acc[0][j][2 * half], fn));
+        if (n + 1 < N) o[1] = __float2bfloat16_rn(plain_act(acc[0][j][2 * half + 1], fn));
       } else if (GATED) {
         const float g0 = acc[0][j][2 * half], g1 = acc[0][j][2 * half + 1];
         const float v0 = g0 / (1.f + expf(-g0)) * acc[GATED ? 1 : 0][j][2 * half];
@@ -479,19 +499,30 @@ int tb_moe_route(void* stream, const float* logits, const float* bias, int* ids,
                     stream, logits, bias, ids, weights, T_tokens, E, top, score, normalize, scale);
 }
 
+// Routing without a router: ids[t, k] = table[token[t], k], every weight 1 / top.  table int32 [vocab, top].
+int tb_moe_route_table(void* stream, const int* tokens, const int* table, int* ids, float* weights, int T_tokens, int top, int vocab,
+                       int E) {
+  if (T_tokens <= 0) return 0;
+  if (top <= 0 || vocab <= 0 || E <= 0) return TB_ERR_BAD_SIZE;
+  const long long total = (long long)T_tokens * top;
+  return tb::launch(tb::route_table_kernel, dim3((int)((total + 255) / 256)), dim3(256), 0, stream, tokens, table, ids, weights, total,
+                    top, vocab, E);
+}
+
 // x [T, K], act [T top, F] of the activations' type `dtype`; the weights of type `dtype` too: w [real, 2 F, K] (gate rows,
-// then up rows) with `gated`, else [real, F, K] and the exact GELU.  Slots whose expert is `real` or more are left out.
+// then up rows) with `gated` = 1, else [real, F, K] and an activation without a gate: `gated` = 0 the exact GELU, -1 the square
+// of max(v, 0).  Slots whose expert is `real` or more are left out.
 // order: int32 [T top] (the slots sorted by expert, so that an expert's rows are fetched once for slots that share it) or null.
 int tb_moe_gate_up(void* stream, const void* x, const void* w, const int* ids, const int* order, void* act, int T_tokens, int top,
                    int F, int K, int real, int gated, int dtype) {
   if (T_tokens <= 0) return 0;
   if (top <= 0 || F <= 0 || K <= 0 || (long long)T_tokens * top > 65535 || K * sizeof(float) > 48 * 1024) return TB_ERR_BAD_SIZE;
   const dim3 grid((F + 8 * tb::EX_PER_WARP - 1) / (8 * tb::EX_PER_WARP), T_tokens * top);
-  if (gated)
+  if (gated > 0)
     TB_DISPATCH_DTYPE(dtype, tb::launch(tb::expert_gate_up_kernel<T, T>, grid, dim3(256), (size_t)K * sizeof(float), stream,
                                         (const T*)x, (const T*)w, ids, order, (T*)act, top, F, K, real));
   TB_DISPATCH_DTYPE(dtype, tb::launch(tb::expert_up_kernel<T, T>, grid, dim3(256), (size_t)K * sizeof(float), stream, (const T*)x,
-                                      (const T*)w, ids, order, (T*)act, top, F, K, real));
+                                      (const T*)w, ids, order, (T*)act, top, F, K, real, gated < 0 ? 2 : 1));
 }
 
 // act [T top, F], w [real, N, F] of type `dtype`; part float32 [T top, N].
@@ -539,13 +570,13 @@ int tb_moe_tiles(void* stream, const void* x, const void* w_gate_up, const void*
   if (rc != 0) return rc;
   const int row_tiles = capacity / tb::ET_M;
   const dim3 up_grid((F + tb::ET_N - 1) / tb::ET_N, row_tiles);
-  rc = gated ? tb::launch(tb::expert_tiles_kernel<1>, up_grid, dim3(128), 0, stream, (const __nv_bfloat16*)x,
-                          (const __nv_bfloat16*)w_gate_up, offsets, sorted, act, top, E, F, K, real)
-             : tb::launch(tb::expert_tiles_kernel<2>, up_grid, dim3(128), 0, stream, (const __nv_bfloat16*)x,
-                          (const __nv_bfloat16*)w_gate_up, offsets, sorted, act, top, E, F, K, real);
+  rc = gated > 0 ? tb::launch(tb::expert_tiles_kernel<1>, up_grid, dim3(128), 0, stream, (const __nv_bfloat16*)x,
+                              (const __nv_bfloat16*)w_gate_up, offsets, sorted, act, top, E, F, K, real, 0)
+                 : tb::launch(tb::expert_tiles_kernel<2>, up_grid, dim3(128), 0, stream, (const __nv_bfloat16*)x,
+                              (const __nv_bfloat16*)w_gate_up, offsets, sorted, act, top, E, F, K, real, gated < 0 ? 2 : 1);
   if (rc != 0) return rc;
   rc = tb::launch(tb::expert_tiles_kernel<0>, dim3((N + tb::ET_N - 1) / tb::ET_N, row_tiles), dim3(128), 0, stream,
-                  (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, offsets, sorted, part, top, E, N, F, real);
+                  (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, offsets, sorted, part, top, E, N, F, real, 0);
   if (rc != 0) return rc;
   return combine(stream, part, weights, nullptr, y, T_tokens, top, N, real < E ? ids : nullptr, real, x, TB_BF16);
 }

@@ -193,8 +193,9 @@ short_conv_kernel(const float* __restrict__ x, const float* __restrict__ taps, i
 
 // One thread per (request, channel): the request's last K - 1 inputs after this step, oldest first.  An entry that
 // still comes from before the step moves down by the number of new tokens; it is read before any turn writes it.
-__global__ void short_conv_state_kernel(const float* __restrict__ x, int W, float* __restrict__ state, long long state_stride,
-                                        const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots, int requests, int K) {
+__global__ void short_conv_state_kernel(const float* __restrict__ x, long long x_stride, int W, float* __restrict__ state,
+                                        long long state_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots,
+                                        int requests, int K) {
   pdl_launch_dependents();
   pdl_wait();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -205,7 +206,7 @@ __global__ void short_conv_state_kernel(const float* __restrict__ x, int W, floa
   float* st = state + (size_t)state_slots[b] * state_stride;
   for (int k = 0; k < K - 1; ++k) {
     const int i = n - (K - 1) + k;
-    st[(size_t)k * W + c] = i >= 0 ? x[(size_t)(t0 + i) * W + c] : st[(size_t)(k + n) * W + c];
+    st[(size_t)k * W + c] = i >= 0 ? x[(size_t)(t0 + i) * x_stride + c] : st[(size_t)(k + n) * W + c];
   }
 }
 
@@ -471,12 +472,19 @@ int tb_short_conv(void* stream, const float* x, const float* taps, int K, const 
   return tb::launch_walk(stream, a, dtype, TB_F32);
 }
 
+// x: rows x_stride floats apart, of which the first W columns are the convolution's inputs.
+int tb_short_conv_state_rows(void* stream, const float* x, long long x_stride, int W, float* state, long long state_stride,
+                             const int* cu_seqlens, const int* state_slots, int requests, int K) {
+  if (requests <= 0 || K <= 1) return 0;
+  if (x_stride < W) return TB_ERR_BAD_SIZE;
+  const long long total = (long long)requests * W;
+  return tb::launch(tb::short_conv_state_kernel, dim3((int)((total + 255) / 256)), dim3(256), 0, stream, x, x_stride, W, state,
+                    state_stride, cu_seqlens, state_slots, requests, K);
+}
+
 int tb_short_conv_state(void* stream, const float* x, int W, float* state, long long state_stride, const int* cu_seqlens,
                         const int* state_slots, int requests, int K) {
-  if (requests <= 0 || K <= 1) return 0;
-  const long long total = (long long)requests * W;
-  return tb::launch(tb::short_conv_state_kernel, dim3((int)((total + 255) / 256)), dim3(256), 0, stream, x, W, state, state_stride,
-                    cu_seqlens, state_slots, requests, K);
+  return tb_short_conv_state_rows(stream, x, W, W, state, state_stride, cu_seqlens, state_slots, requests, K);
 }
 
 // inv [T, groups] = 1 / sqrt(mean(run^2) + eps) of the runs of y's rows (float32 or bfloat16 by y_dtype).

@@ -104,13 +104,18 @@ __device__ __forceinline__ float key_dot(const float* qs, const T* tile, int r, 
   return dot;
 }
 
+// The output gate of a head: sigmoid of one number per (token, head), float32 rows `stride` apart.
+__device__ __forceinline__ float head_gate(const float* gate, int stride, int t, int h) {
+  return 1.f / (1.f + expf(-gate[(size_t)t * stride + h]));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(SA_WARPS * 32)
 sink_attention_kernel(const float* __restrict__ q, int q_stride, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                       const int* __restrict__ block_table, int table_stride, const int* __restrict__ seq_of_token,
                       const int* __restrict__ positions, T* __restrict__ out, int T_tokens, int nh, int nkv, int dk, int dv,
                       int page_size, int window, int keep_first, float scale, float cap, const float* __restrict__ bias,
-                      int max_dist, const float* __restrict__ sink) {
+                      int max_dist, const float* __restrict__ sink, const float* __restrict__ gate, int gate_stride) {
   extern __shared__ float smem[];  // SA_WARPS * dk floats: each warp's query
   pdl_launch_dependents();
   pdl_wait();
@@ -174,7 +179,8 @@ sink_attention_kernel(const float* __restrict__ q, int q_stride, const T* __rest
       }
     }
   }
-  const float inv = l > 0.f ? 1.f / l : 0.f;
+  float inv = l > 0.f ? 1.f / l : 0.f;
+  if (gate) inv *= head_gate(gate, gate_stride, t, h);
   T* orow = out + (size_t)t * nh * dv + (size_t)h * dv;
 #pragma unroll
   for (int i = 0; i < MAX_OWN; ++i) {
@@ -404,7 +410,8 @@ sink_attention_split_kernel(const float* __restrict__ q, int q_stride, const T* 
 // One warp per (token, head): the sink, then the splits in order.
 template <typename T>
 __global__ void sink_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                            const float* __restrict__ sink, T* __restrict__ out, int rows, int nh, int dv, int splits) {
+                                            const float* __restrict__ sink, T* __restrict__ out, int rows, int nh, int dv, int splits,
+                                            const float* __restrict__ gate, int gate_stride) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -417,7 +424,8 @@ __global__ void sink_attention_merge_kernel(const float* __restrict__ part_o, co
   const float mm = fmaxf(sink ? sink[h] : -INFINITY, warp_max(ms));
   const float f = ms == -INFINITY ? 0.f : expf(ms - mm);
   const float ll = warp_sum(ls * f) + (sink ? expf(sink[h] - mm) : 0.f);
-  const float inv = ll > 0.f ? 1.f / ll : 0.f;
+  float inv = ll > 0.f ? 1.f / ll : 0.f;
+  if (gate) inv *= head_gate(gate, gate_stride, row / nh, h);
   for (int d = lane; d < dv; d += 32) {
     float o = 0.f;
 #pragma unroll 8
@@ -426,9 +434,180 @@ __global__ void sink_attention_merge_kernel(const float* __restrict__ part_o, co
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// `attention_prepare`: everything between the projection and the attention for mixers whose queries and
+// keys are convolved, normed with a weight and rotated.  One block of four warps per token.  The token's
+// row of the float32 projection, columns [q: nh dk | k: nkv dk | v: nkv dv] (k and v absent where the
+// keys and values are another layer's, v absent where the values are the keys as projected), goes through
+//   1. the projection bias, and a causal convolution over time per column, u_t = sum_j w[c, j] x_(t - K + 1 + j):
+//      inputs of the same step come from the rows in front, older ones from the request's state (its last
+//      K - 1 rows, oldest first; zeroed at admission, which makes the zeros in front of a sequence);
+//   2. a norm of q and of k: none; per head without a weight; per head with one weight of dk numbers for all
+//      heads; or over the whole of q (of k) with a weight of that size: x / sqrt(mean(x^2) + eps) * w;
+//   3. the rotation of the first `rot` numbers of each q and k head, number i paired with i + rot / 2, by the
+//      angle position * freq[i] (float32; the host makes the frequency table);
+// and leaves q in `q_out` (float32 [T, nh dk]) and k and v in the token's cache slot.  The values that go
+// into the cache are step 1's, before the norm (also where they are the keys').
+struct PrepareArgs {
+  const float* proj;
+  long long stride;
+  const float* bias;   // [columns] or null
+  const float* taps;   // [columns, K] or null
+  int K;
+  const float* state;  // rows of state_stride floats: [K - 1, columns]
+  long long state_stride;
+  const float* q_w;
+  const float* k_w;
+  int norm;  // 0 none, 1 per head without weight, 2 per head with a shared weight, 3 over all heads with a weight
+  float eps;
+  const float* freq;  // [rot / 2] or null
+  int rot;
+  const int* positions;
+  const int* seq_of_token;
+  const int* seq_starts;
+  const int* state_slots;
+  const int* slots;
+  float* q_out;
+  void* k_cache;
+  void* v_cache;
+  int nh, nkv, dk, dv, page_size;
+  int has_kv, v_from_k, write_kv;
+};
+
+constexpr int AP_NONE = 0, AP_UNIT = 1, AP_HEAD = 2, AP_WHOLE = 3;
+
+template <typename T>
+__global__ void __launch_bounds__(128) attention_prepare_kernel(PrepareArgs a) {
+  extern __shared__ float u[];  // the token's row after step 1
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int q_cols = a.nh * a.dk, k_cols = a.has_kv ? a.nkv * a.dk : 0;
+  const int v_cols = (a.has_kv && !a.v_from_k) ? a.nkv * a.dv : 0;
+  const int cols = q_cols + k_cols + v_cols;
+  const int pos = a.positions[t];
+  const float* row = a.proj + (size_t)t * a.stride;
+  if (a.taps && a.K > 0) {
+    const int b = a.seq_of_token[t], start = a.seq_starts[b], K = a.K;
+    const float* st = a.K > 1 ? a.state + (size_t)a.state_slots[b] * a.state_stride : nullptr;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+      const float bc = a.bias ? a.bias[c] : 0.f;
+      float acc = 0.f;
+      for (int j = 0; j < K; ++j) {  // oldest input first
+        const int back = K - 1 - j, pp = pos - back;
+        if (pp < 0) continue;
+        const float x = pp >= start ? row[c - (long long)back * a.stride] : st[(size_t)(pp - start + K - 1) * cols + c];
+        acc = fmaf(a.taps[(size_t)c * K + j], x + bc, acc);
+      }
+      u[c] = acc;
+    }
+  } else {
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) u[c] = row[c] + (a.bias ? a.bias[c] : 0.f);
+  }
+  __syncthreads();
+  float inv_q = 1.f, inv_k = 1.f;
+  if (a.norm == AP_WHOLE) {
+    float sq = 0.f, sk = 0.f;
+    for (int c = threadIdx.x; c < q_cols; c += blockDim.x) sq += u[c] * u[c];
+    for (int c = threadIdx.x; c < k_cols; c += blockDim.x) sk += u[q_cols + c] * u[q_cols + c];
+    inv_q = rsqrtf(block_sum(sq, scratch) / (float)q_cols + a.eps);
+    if (k_cols) inv_k = rsqrtf(block_sum(sk, scratch) / (float)k_cols + a.eps);
+  }
+  const int slot = (a.has_kv && a.write_kv && a.slots) ? a.slots[t] : -1;
+  const int units = a.nh + (a.has_kv ? a.nkv : 0) + (v_cols ? a.nkv : 0);
+  const int dk = a.dk, dv = a.dv, half = a.rot / 2;
+  for (int unit = warp; unit < units; unit += 4) {
+    if (unit >= a.nh + a.nkv) {  // a value head of its own
+      if (slot < 0) continue;
+      const int kvh = unit - a.nh - a.nkv;
+      const float* x = u + q_cols + k_cols + kvh * dv;
+      T* tile = reinterpret_cast<T*>(a.v_cache) + cache_tile(slot / a.page_size, kvh, a.nkv, a.page_size, dv);
+      const int r = slot % a.page_size;
+      for (int d = lane; d < dv; d += 32) tile[cache_offset<T>(r, d, a.page_size, dv)] = from_float<T>(x[d]);
+      continue;
+    }
+    const bool is_q = unit < a.nh;
+    const int kvh = unit - a.nh;
+    if (!is_q && slot < 0) continue;
+    float* x = u + unit * dk;  // q heads, then k heads, lie one behind the other
+    if (!is_q && a.v_from_k) {  // the values are the keys as they stand now
+      T* tile = reinterpret_cast<T*>(a.v_cache) + cache_tile(slot / a.page_size, kvh, a.nkv, a.page_size, dv);
+      const int r = slot % a.page_size;
+      for (int d = lane; d < dv; d += 32) tile[cache_offset<T>(r, d, a.page_size, dv)] = from_float<T>(x[d]);
+    }
+    if (a.norm != AP_NONE) {
+      float inv = is_q ? inv_q : inv_k;
+      if (a.norm != AP_WHOLE) {
+        float ss = 0.f;
+        for (int d = lane; d < dk; d += 32) ss += x[d] * x[d];
+        inv = rsqrtf(warp_sum(ss) / (float)dk + a.eps);
+      }
+      const float* w = is_q ? a.q_w : a.k_w;
+      if (a.norm == AP_WHOLE) w += is_q ? unit * dk : kvh * dk;
+      const bool weighted = a.norm == AP_HEAD || a.norm == AP_WHOLE;
+      for (int d = lane; d < dk; d += 32) x[d] = x[d] * inv * (weighted ? w[d] : 1.f);
+    }
+    __syncwarp();
+    float* q_dst = is_q ? a.q_out + (size_t)t * q_cols + (size_t)unit * dk : nullptr;
+    T* tile = is_q ? nullptr : reinterpret_cast<T*>(a.k_cache) + cache_tile(slot / a.page_size, kvh, a.nkv, a.page_size, dk);
+    const int r = is_q ? 0 : slot % a.page_size;
+    for (int d = lane; d < dk; d += 32) {
+      float y = x[d];
+      if (d < a.rot) {
+        const int i = d < half ? d : d - half;
+        float sn, cs;
+        sincosf((float)pos * a.freq[i], &sn, &cs);
+        y = d < half ? x[d] * cs - x[d + half] * sn : x[d] * cs + x[d - half] * sn;
+      }
+      if (is_q) q_dst[d] = y;
+      else tile[cache_offset<T>(r, d, a.page_size, dk)] = from_float<T>(y);
+    }
+  }
+}
+
 }  // namespace tb
 
 extern "C" {
+
+// See attention_prepare_kernel.  proj float32 rows `stride` floats apart; bias float32 [columns] or null; taps float32
+// [columns, K] or null (then K = 0); state float32 rows of state_stride >= (K - 1) columns floats, indexed by state_slots
+// of the token's request (seq_of_token, seq_starts: the tokens a request had before this step); q_w / k_w by `norm`:
+// 0 and 1 none, 2 [dk], 3 [nh dk] / [nkv dk]; freq float32 [rot / 2] or null (rot = 0); q_out float32 [T, nh dk];
+// caches of the storage type `dtype`.  has_kv 0: the projection has no key or value columns.  v_from_k needs dv == dk.
+int tb_attention_prepare(void* stream, const float* proj, long long stride, const float* bias, const float* taps, int K,
+                         const float* state, long long state_stride, const float* q_w, const float* k_w, int norm, float eps,
+                         const float* freq, int rot, const int* positions, const int* seq_of_token, const int* seq_starts,
+                         const int* state_slots, const int* slots, float* q_out, void* k_cache, void* v_cache, int T_tokens, int nh,
+                         int nkv, int dk, int dv, int page_size, int has_kv, int v_from_k, int write_kv, int dtype) {
+  if (T_tokens <= 0) return 0;
+  if (nh <= 0 || nkv <= 0 || dk <= 0 || dv <= 0 || page_size <= 0 || norm < 0 || norm > 3 || rot < 0 || rot > dk || (rot & 1) ||
+      (rot && !freq) || K < 0 || (K > 0 && !taps) || (K > 1 && !state) || (v_from_k && dv != dk) ||
+      (norm >= 2 && (!q_w || (has_kv && !k_w))))
+    return TB_ERR_BAD_SIZE;
+  const long long cols = (long long)nh * dk + (has_kv ? (long long)nkv * dk + (v_from_k ? 0 : (long long)nkv * dv) : 0);
+  const size_t smem = (size_t)cols * sizeof(float);
+  if (smem > 200 * 1024 || (K > 1 && state_stride < (long long)(K - 1) * cols)) return TB_ERR_BAD_SIZE;
+  tb::PrepareArgs a;
+  a.proj = proj; a.stride = stride; a.bias = bias; a.taps = K > 0 ? taps : nullptr; a.K = K; a.state = state; a.state_stride = state_stride;
+  a.q_w = q_w; a.k_w = k_w; a.norm = norm; a.eps = eps; a.freq = freq; a.rot = rot; a.positions = positions;
+  a.seq_of_token = seq_of_token; a.seq_starts = seq_starts; a.state_slots = state_slots; a.slots = slots; a.q_out = q_out;
+  a.k_cache = k_cache; a.v_cache = v_cache; a.nh = nh; a.nkv = nkv; a.dk = dk; a.dv = dv; a.page_size = page_size;
+  a.has_kv = has_kv; a.v_from_k = v_from_k; a.write_kv = write_kv;
+  if (dtype != TB_F32 && dtype != TB_BF16) return TB_ERR_BAD_DTYPE;
+  if (smem > 48 * 1024) {  // per storage type: the attribute belongs to the instantiation
+    static size_t allowed[2] = {0, 0};
+    if (allowed[dtype] < smem) {
+      cudaError_t e = dtype == TB_F32
+          ? cudaFuncSetAttribute(tb::attention_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+          : cudaFuncSetAttribute(tb::attention_prepare_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      allowed[dtype] = smem;
+    }
+  }
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::attention_prepare_kernel<T>, dim3(T_tokens), dim3(128), smem, stream, a));
+}
 
 // qkv float32 [T, stride >= nh dk + nkv dk + nkv dv]; bias float32 [nh dk + nkv dk + nkv dv] or null;
 // v_other float32 rows of nkv dv values (stride v_other_stride) with mix[0] their share, or null;
@@ -445,10 +624,11 @@ int tb_sink_attention_prep(void* stream, float* qkv, int stride, const float* bi
                                       unit_norm, eps, write_kv));
 }
 
+// gate: float32 rows of one number per query head (gate_stride floats apart), whose sigmoid multiplies the head's output; or null.
 int tb_sink_attention(void* stream, const float* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
                       int table_stride, const int* seq_of_token, const int* positions, void* out, int T_tokens, int nh, int nkv,
                       int dk, int dv, int page_size, int window, int keep_first, float scale, float cap, const float* bias,
-                      int max_dist, const float* sink, int dtype) {
+                      int max_dist, const float* sink, int dtype, const float* gate, int gate_stride) {
   if (T_tokens <= 0) return 0;
   if (dk <= 0 || dv <= 0 || dv > tb::SA_MAX_DV || dk > 2048 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || window < 0 ||
       keep_first < 0 || (bias && max_dist < 0))
@@ -459,16 +639,16 @@ int tb_sink_attention(void* stream, const float* q, int q_stride, const void* k_
   TB_DISPATCH_DTYPE(dtype, tb::launch(tb::sink_attention_kernel<T>, dim3(blocks), dim3(tb::SA_WARPS * 32), smem, stream, q, q_stride,
                                       (const T*)k_cache, (const T*)v_cache, block_table, table_stride, seq_of_token, positions,
                                       (T*)out, T_tokens, nh, nkv, dk, dv, page_size, window, keep_first, scale, cap, bias, max_dist,
-                                      sink));
+                                      sink, gate, gate_stride));
 }
 
 // The same attention for steps of single tokens, cut over `splits` blocks per (token, kv head):
-// part_o float32 [T nh splits dv], part_ml float32 [T nh splits 2] are scratch.
+// part_o float32 [T nh splits dv], part_ml float32 [T nh splits 2] are scratch.  gate as in tb_sink_attention.
 int tb_sink_attention_split(void* stream, const float* q, int q_stride, const void* k_cache, const void* v_cache,
                             const int* block_table, int table_stride, const int* seq_of_token, const int* positions, void* out,
                             float* part_o, float* part_ml, int splits, int T_tokens, int nh, int nkv, int dk, int dv, int page_size,
                             int window, int keep_first, float scale, float cap, const float* bias, int max_dist, const float* sink,
-                            int dtype) {
+                            int dtype, const float* gate, int gate_stride) {
   if (T_tokens <= 0) return 0;
   if (dk <= 0 || dv <= 0 || dv > 32 * tb::SD_MAX_OWN || (dk & 3) || nkv <= 0 || nh % nkv != 0 || page_size <= 0 ||
       window < 0 || keep_first < 0 || splits <= 0 || splits > 32 || T_tokens > 65535 || nkv > 65535 || (q_stride & 3) || (bias && max_dist < 0))
@@ -493,7 +673,7 @@ int tb_sink_attention_split(void* stream, const float* q, int q_stride, const vo
   if (rc != 0) return rc;
   const int rows = T_tokens * nh;
   TB_DISPATCH_DTYPE(dtype, tb::launch(tb::sink_attention_merge_kernel<T>, dim3((rows + 3) / 4), dim3(128), 0, stream, part_o, part_ml,
-                                      sink, (T*)out, rows, nh, dv, splits));
+                                      sink, (T*)out, rows, nh, dv, splits, gate, gate_stride));
 }
 
 }  // extern "C"

@@ -42,6 +42,8 @@ struct TileArgs {
   float scale, cap;
   const float* bias;
   const float* sink;
+  const float* gate;  // one number per (token, query head), rows gate_stride floats apart: its sigmoid multiplies the head's output
+  int gate_stride;
 };
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
@@ -244,7 +246,8 @@ __global__ void __launch_bounds__(ST_THREADS) sink_attention_tile_kernel(const T
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     if (tl_row[r] >= ntok) continue;
-    const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+    float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+    if (a.gate) inv *= 1.f / (1.f + expf(-a.gate[(size_t)(t0 + tl_row[r]) * a.gate_stride + head[r]]));
     __nv_bfloat16* dst = a.out + (size_t)(t0 + tl_row[r]) * a.nh * DV + (size_t)head[r] * DV + (lane & 3) * 2;
 #pragma unroll
     for (int j = 0; j < DV / 8; ++j)
@@ -264,7 +267,7 @@ int tb_sink_attention_tile_rows() { return tb::ST_BM; }
 int tb_sink_attention_tile(void* stream, const float* q, int q_stride, const void* k_cache, const void* v_cache,
                            const int* block_table, int table_stride, const int* tiles, int num_tiles, void* out, int nh, int nkv,
                            int page_size, int window, int keep_first, float scale, float cap, const float* bias, int max_dist,
-                           const float* sink) {
+                           const float* sink, const float* gate, int gate_stride) {
   if (num_tiles <= 0) return 0;
   if (nkv <= 0 || nh % nkv != 0 || nh / nkv > tb::ST_BM || page_size <= 0 || window < 0 || keep_first < 0 || (q_stride & 3) ||
       (bias && max_dist < 0) || nkv > 65535)
@@ -275,7 +278,7 @@ int tb_sink_attention_tile(void* stream, const float* q, int q_stride, const voi
   a.block_table = block_table; a.table_stride = table_stride;
   a.tiles = tiles; a.out = (__nv_bfloat16*)out;
   a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window; a.keep_first = window > 0 ? keep_first : 0; a.max_dist = max_dist;
-  a.scale = scale; a.cap = cap; a.bias = bias; a.sink = sink;
+  a.scale = scale; a.cap = cap; a.bias = bias; a.sink = sink; a.gate = gate; a.gate_stride = gate_stride;
   static bool configured = false;
   const size_t smem = tb::tile_smem_bytes();
   if (!configured && smem > 48 * 1024) {

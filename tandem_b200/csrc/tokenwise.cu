@@ -447,6 +447,7 @@ __global__ void scale_softcap_kernel(float* __restrict__ x, long long n, float s
 __device__ __forceinline__ float bias_act_one(float z, int act) {
   if (act == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
   if (act == 2) return z / (1.f + expf(-z));
+  if (act == 3) { const float r = fmaxf(z, 0.f); return r * r; }
   return z;
 }
 
@@ -506,9 +507,96 @@ __global__ void add_pair_kernel(float* __restrict__ residual, const float* __res
   }
 }
 
+
+__device__ __forceinline__ void load4(const float* p, float* v) {
+  const float4 f = *reinterpret_cast<const float4*>(p);
+  v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float* v) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) { *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d); }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+  *reinterpret_cast<uint2*>(p) = make_uint2(pack2(a, b), pack2(c, d));
+}
+
+// A sublayer's output normed and added into the stream, and the stream normed for the next sublayer, one block per row:
+//   v = residual[src] + y[src] * rsqrt(mean(y[src]^2) + y_eps) * y_w        (written back to residual[src])
+//   out[r] = v * rsqrt(mean(v^2) + eps) * w                                 (w null: no out)
+// with src = rows ? rows[r] : r.  All sums in float32, in an order that the row's length alone decides.
+template <typename Y, typename O>
+__global__ void norm_add_norm_kernel(const Y* __restrict__ y, const float* __restrict__ y_w, float y_eps, float* __restrict__ residual,
+                                     const float* __restrict__ w, float eps, O* __restrict__ out, const int* __restrict__ rows, int H) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  const Y* yr = y + (size_t)src * H;
+  float* res = residual + (size_t)src * H;
+  float ss = 0.f;
+  if ((H & 3) == 0) {  // four numbers a turn
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float v[4];
+      load4(yr + i, v);
+      ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+    }
+    const float inv_y = rsqrtf(block_sum(ss, scratch) / (float)H + y_eps);
+    ss = 0.f;
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float v[4];
+      load4(yr + i, v);
+      const float4 g = *reinterpret_cast<const float4*>(y_w + i);
+      float4 x = *reinterpret_cast<const float4*>(res + i);
+      x.x += v[0] * inv_y * g.x; x.y += v[1] * inv_y * g.y; x.z += v[2] * inv_y * g.z; x.w += v[3] * inv_y * g.w;
+      *reinterpret_cast<float4*>(res + i) = x;
+      ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+    }
+    if (!w) return;
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)H + eps);
+    O* o = out + (size_t)r * H;
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {  // each thread reads back what it wrote itself
+      const float4 x = *reinterpret_cast<const float4*>(res + i), g = *reinterpret_cast<const float4*>(w + i);
+      store4(o + i, x.x * inv * g.x, x.y * inv * g.y, x.z * inv * g.z, x.w * inv * g.w);
+    }
+    return;
+  }
+  for (int i = threadIdx.x; i < H; i += blockDim.x) { const float v = to_float(yr[i]); ss += v * v; }
+  const float inv_y = rsqrtf(block_sum(ss, scratch) / (float)H + y_eps);
+  ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float x = res[i] + to_float(yr[i]) * inv_y * y_w[i];
+    res[i] = x;
+    ss += x * x;
+  }
+  if (!w) return;
+  const float inv = rsqrtf(block_sum(ss, scratch) / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)r * H + i] = from_float<O>(res[i] * inv * w[i]);
+}
+
 }  // namespace tb
 
 extern "C" {
+
+// See norm_add_norm_kernel.  y [T, H] float32 or bfloat16 (y_dtype); out [num_rows, H] float32 or bfloat16 (dtype), or
+// null with w null (the add alone).
+int tb_norm_add_norm(void* stream, const void* y, int y_dtype, const float* y_w, float y_eps, float* residual, const float* w, float eps,
+                     void* out, const int* rows, int num_rows, int H, int dtype) {
+  if (num_rows <= 0) return 0;
+  if (H <= 0 || (w && !out)) return TB_ERR_BAD_SIZE;
+  const int threads = H >= 4096 ? 512 : 256;
+#define TB_NAN(YT, OT)                                                                                                      \
+  return tb::launch(tb::norm_add_norm_kernel<YT, OT>, dim3(num_rows), dim3(threads), 0, stream, (const YT*)y, y_w, y_eps, \
+                    residual, w, eps, (OT*)out, rows, H)
+  if (y_dtype == TB_F32 && dtype == TB_F32) TB_NAN(float, float);
+  if (y_dtype == TB_F32 && dtype == TB_BF16) TB_NAN(float, __nv_bfloat16);
+  if (y_dtype == TB_BF16 && dtype == TB_F32) TB_NAN(__nv_bfloat16, float);
+  if (y_dtype == TB_BF16 && dtype == TB_BF16) TB_NAN(__nv_bfloat16, __nv_bfloat16);
+#undef TB_NAN
+  return TB_ERR_BAD_DTYPE;
+}
 
 // positions / pos_table [max_pos, H] may be null (no learned absolute positions).
 int tb_embedding(void* stream, const int* ids, const void* table, float* out, int T_tokens, int H, int V,
@@ -576,7 +664,7 @@ int tb_silu_mul(void* stream, const void* gu, void* out, int T_tokens, int I, in
 int tb_bias_act(void* stream, const float* x, const float* bias, void* y, int rows, int N, int act, int dtype) {
   const long long total = (long long)rows * N;
   if (total <= 0) return 0;
-  if (act < 0 || act > 2) return TB_ERR_BAD_SIZE;
+  if (act < 0 || act > 3) return TB_ERR_BAD_SIZE;
   long long blocks = (total / 4 + 255) / 256 + 1;
   if (blocks > 148 * 16) blocks = 148 * 16;
   TB_DISPATCH_DTYPE(dtype, tb::launch(tb::bias_act_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, x, bias, (T*)y, total, N, act));

@@ -25,6 +25,10 @@ that travels between the parts of a layer must be allowed to be *not computed ye
                    kernel (``ops.stream_norm``).  It stands for no tensor: only arrangements that keep such a
                    residual hand it on.
 
+``Normed``         a sublayer's output y that has still to be normed (y / rms(y) * weight) and added into the stream: what
+                   an arrangement with norms on both sides of its sublayers hands on, so that the norm in front of the
+                   next sublayer does "norm, add, norm" in one kernel (``ops.norm_add_norm``).
+
 Only parts that say ``takes_deferred = True`` ever meet one of these; everything else gets tensors
 (``tensor`` computes what is pending with the stand-alone kernels).  12vivi/tandem fuses the same
 pair into its small-batch product (python/tandem/layers/triton_gemv.py:92-145,356-378).
@@ -86,8 +90,19 @@ class StreamWrite:
         return tuple(self.y.shape)
 
 
+@dataclass
+class Normed:
+    y: torch.Tensor  # [M, H] float32 or the model's type
+    weight: torch.Tensor  # [H] float32
+    eps: float
+
+    @property
+    def shape(self) -> tuple:
+        return tuple(self.y.shape)
+
+
 def is_pending(v: Any) -> bool:
-    return isinstance(v, (PendingLinear, PendingNorm, Unsummed, StreamWrite))
+    return isinstance(v, (PendingLinear, PendingNorm, Unsummed, StreamWrite, Normed))
 
 
 def tensor(v: Any) -> Optional[torch.Tensor]:
@@ -102,6 +117,11 @@ def tensor(v: Any) -> Optional[torch.Tensor]:
         return ops.add_rmsnorm(None, v.residual, v.weight, v.eps, v.out_dtype)
     if isinstance(v, Unsummed):
         return ops.bias_act(v.product, v.bias, "none", v.out_dtype)
+    if isinstance(v, Normed):
+        from tandem_b200.kernels import post_norm
+
+        y = v.y if v.y.dtype == torch.float32 else v.y.float()
+        return post_norm.group_norm(y, v.weight, 1, v.eps, torch.float32)
     if isinstance(v, StreamWrite):
         raise TypeError("a write into a residual of several streams stands for no tensor: the arrangement behind it must "
                         "keep such a residual (its norm does the write)")

@@ -123,9 +123,9 @@ def wide_grouped(x: torch.Tensor, weight: torch.Tensor, tile_group: torch.Tensor
     """``wide`` with a weight per group of rows: ``weight`` [groups * N, K] holds the groups' matrices one behind
     the other, every 128 rows of ``x`` belong to the group ``tile_group[tile]`` (int32 on the device; -1: the tile
     holds no rows, nothing is computed or written for it).  Returns [M, N] (``gated``: [M, N / 2]).
-    ``activation`` "gelu" (bfloat16 output without a gate): the exact GELU in the epilogue."""
-    if activation not in ("none", "gelu"):
-        raise ops.KernelError(f"the grouped product has no activation {activation!r} (none or gelu)")
+    ``activation`` (bfloat16 output without a gate) in the epilogue: "gelu" the exact GELU, "relu2" the square of max(z, 0)."""
+    if activation not in ("none", "gelu", "relu2"):
+        raise ops.KernelError(f"the grouped product has no activation {activation!r} (none, gelu or relu2)")
     M, K = x.shape
     N = weight.shape[0] // groups
     if weight.shape[0] != N * groups or weight.shape[1] != K or M % 128 or tile_group.numel() != M // 128:
@@ -135,7 +135,7 @@ def wide_grouped(x: torch.Tensor, weight: torch.Tensor, tile_group: torch.Tensor
     lib = load_library("gemm_wide")
     ops._check(lib.tb_gemm_wide_grouped_act(ops._stream(), ops._ptr(x), ops._ptr(weight), ops._ptr(y),
                                             ops._ptr(ops.status_word(x.device)), M, N, K, int(out_dtype == torch.float32), int(gated),
-                                            sm_count(x.device), ops._ptr(tile_group), groups, int(activation == "gelu")),
+                                            sm_count(x.device), ops._ptr(tile_group), groups, {"none": 0, "gelu": 1, "relu2": 2}[activation]),
                "gemm_wide_grouped")
     return y
 

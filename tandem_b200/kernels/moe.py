@@ -48,6 +48,33 @@ def route(logits: torch.Tensor, top_k: int, score: str, normalize: bool, scale: 
     return ids, weights
 
 
+def route_table(token_ids: torch.Tensor, table: torch.Tensor, num_experts: int) -> tuple:
+    """Routing without a router: token ids int32 [T] and a table int32 [vocab, top] -> (experts int32 [T, top] =
+    table[token], weights float32 [T, top], each 1 / top)."""
+    ops._need(token_ids, "token_ids", torch.int32)
+    ops._need(table, "table", torch.int32)
+    if table.dim() != 2:
+        raise ops.KernelError(f"the experts' table has shape {tuple(table.shape)}, expected [vocab, top]")
+    T, (vocab, top) = token_ids.numel(), table.shape
+    ids = torch.empty((T, top), dtype=torch.int32, device=table.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=table.device)
+    lib = load_library("moe")
+    ops._check(lib.tb_moe_route_table(ops._stream(), ops._ptr(token_ids), ops._ptr(table), ops._ptr(ids), ops._ptr(weights), T, top,
+                                      vocab, int(num_experts)), "moe_route_table")
+    return ids, weights
+
+
+_PLAIN_ACTIVATIONS = {"gelu": 0, "relu2": -1}  # how the kernels are told which activation an expert without a gate has
+
+
+def _gate_code(gated: bool, activation: str) -> int:
+    if gated:
+        return 1
+    if activation not in _PLAIN_ACTIVATIONS:
+        raise ops.KernelError(f"experts without a gate have no activation {activation!r} (have {sorted(_PLAIN_ACTIVATIONS)})")
+    return _PLAIN_ACTIVATIONS[activation]
+
+
 def tiles_apply(x: torch.Tensor, hidden: int, inner: int) -> bool:
     return (x.dtype == torch.bfloat16 and x.shape[0] >= TILE_MIN_TOKENS and hidden % 8 == 0 and inner % 8 == 0
             and ops.env("TANDEM_MOE", "wide") != "simt")
@@ -61,7 +88,7 @@ def wide_applies(x: torch.Tensor, hidden: int, inner: int, top: int, num_experts
             and ops.env("TANDEM_MOE", "wide") not in ("simt", "tiles"))
 
 
-def _experts_wide(x, gate_up, down, ids, weights, gated: bool, E: int) -> torch.Tensor:
+def _experts_wide(x, gate_up, down, ids, weights, gated: bool, E: int, activation: str = "gelu") -> torch.Tensor:
     from tandem_b200.kernels import gemm_bf16
 
     T, K = x.shape
@@ -80,7 +107,7 @@ def _experts_wide(x, gate_up, down, ids, weights, gated: bool, E: int) -> torch.
     if gated:
         act = gemm_bf16.wide_grouped(xs, gate_up.view(real * 2 * F, K), tile_group, real, torch.bfloat16, gated=True)
     else:
-        act = gemm_bf16.wide_grouped(xs, gate_up.view(real * F, K), tile_group, real, torch.bfloat16, activation="gelu")
+        act = gemm_bf16.wide_grouped(xs, gate_up.view(real * F, K), tile_group, real, torch.bfloat16, activation=activation)
     part = gemm_bf16.wide_grouped(act, down.view(real * K, F), tile_group, real, torch.float32, gated=False)
     y = torch.empty((T, K), dtype=torch.float32, device=dev)
     _combine(lib, part, weights, position, y, T, top, K, ids, real, E, x)
@@ -96,11 +123,11 @@ def _combine(lib, part, weights, position, y, T: int, top: int, N: int, ids, rea
 
 
 def experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-            gated: bool = True, num_router_outputs: Optional[int] = None) -> torch.Tensor:
+            gated: bool = True, num_router_outputs: Optional[int] = None, activation: str = "gelu") -> torch.Tensor:
     """sum_k weights[t, k] * down[e] (SiLU(gate[e] x_t) * (up[e] x_t)) with e = ids[t, k]: float32 [T, hidden].
     x [T, hidden]; gate_up [E, 2 F, hidden] (an expert's gate rows, then its up rows); down [E, hidden, F].
-    Without a gate (``gated`` False): ``gate_up`` is up [E, F, hidden] and an expert is down[e] GELU(up[e] x_t), the
-    exact GELU.  ``num_router_outputs`` > E: experts E and above are identity experts, whose slots add weights[t, k] * x_t."""
+    Without a gate (``gated`` False): ``gate_up`` is up [E, F, hidden] and an expert is down[e] act(up[e] x_t), ``activation``
+    "gelu" (the exact one) or "relu2" (the square of max(z, 0)).  ``num_router_outputs`` > E: experts E and above are identity experts, whose slots add weights[t, k] * x_t."""
     ops._need(x, "x")
     ops._need(gate_up, "gate_up", x.dtype)
     ops._need(down, "down", x.dtype)
@@ -113,8 +140,9 @@ def experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: tor
     if K2 != K or tuple(down.shape) != (real, K, F) or tuple(ids.shape) != (T, top) or tuple(weights.shape) != (T, top) or E < real:
         raise ops.KernelError(f"x {tuple(x.shape)}, gate_up {tuple(gate_up.shape)}, down {tuple(down.shape)}, ids "
                               f"{tuple(ids.shape)} do not fit together")
+    code = _gate_code(gated, activation)
     if wide_applies(x, K, F, top, E):
-        return _experts_wide(x, gate_up, down, ids, weights, gated, E)
+        return _experts_wide(x, gate_up, down, ids, weights, gated, E, activation)
     y = torch.empty((T, K), dtype=torch.float32, device=x.device)
     lib = load_library("moe")
     if tiles_apply(x, K, F):
@@ -126,7 +154,7 @@ def experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: tor
         part = torch.empty((T * top, K), dtype=torch.float32, device=x.device)
         ops._check(lib.tb_moe_tiles(ops._stream(), ops._ptr(x), ops._ptr(gate_up), ops._ptr(down), ops._ptr(ids), ops._ptr(weights),
                                     ops._ptr(offsets), ops._ptr(order), ops._ptr(act), ops._ptr(part), ops._ptr(y), T, top, E, K, F, K,
-                                    capacity, real, int(bool(gated))), "moe_tiles")
+                                    capacity, real, code), "moe_tiles")
         ops.launches += 3  # four kernels
         return y
     step = max(1, _MAX_SLOTS // top)
@@ -138,7 +166,7 @@ def experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: tor
         part = torch.empty((n * top, K), dtype=torch.float32, device=x.device)
         ops._check(lib.tb_moe_order(ops._stream(), ops._ptr(ids[t0:]), ops._ptr(offsets), ops._ptr(order), n, top, E), "moe_order")
         ops._check(lib.tb_moe_gate_up(ops._stream(), ops._ptr(x[t0:]), ops._ptr(gate_up), ops._ptr(ids[t0:]), ops._ptr(order),
-                                      ops._ptr(act), n, top, F, K, real, int(bool(gated)), ops._code(x.dtype)), "moe_gate_up")
+                                      ops._ptr(act), n, top, F, K, real, code, ops._code(x.dtype)), "moe_gate_up")
         ops._check(lib.tb_moe_down(ops._stream(), ops._ptr(act), ops._ptr(down), ops._ptr(ids[t0:]), ops._ptr(order), ops._ptr(part),
                                    n, top, K, F, real, ops._code(x.dtype)), "moe_down")
         _combine(lib, part, weights[t0:], None, y[t0:], n, top, K, ids[t0:], real, E, x[t0:])

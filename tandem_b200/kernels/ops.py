@@ -182,6 +182,8 @@ def add_rmsnorm(x, residual: torch.Tensor, weight: torch.Tensor, eps: float,
 
     if isinstance(x, deferred.StreamWrite):
         return stream_norm(residual, x, None, weight, eps, out_dtype, rows)
+    if isinstance(x, deferred.Normed):
+        return norm_add_norm(x.y, x.weight, x.eps, residual, weight, eps, out_dtype, rows)
     if isinstance(x, deferred.PendingLinear):
         if defer and rows is None and out_dtype == torch.bfloat16 and x.shape == tuple(residual.shape) \
                 and gemm_bf16.add_fusable(x.x, x.weight):
@@ -208,6 +210,31 @@ def add_rmsnorm(x, residual: torch.Tensor, weight: torch.Tensor, eps: float,
     _check(lib.tb_add_rmsnorm(_stream(), _ptr(x), _ptr(residual), _ptr(weight), _ptr(y), _ptr(rows), n, H,
                               ctypes.c_float(eps), _code(out_dtype)), "add_rmsnorm")
     return y
+
+
+def norm_add_norm(y: torch.Tensor, y_weight: torch.Tensor, y_eps: float, residual: torch.Tensor, weight: Optional[torch.Tensor],
+                  eps: float, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """residual += y / sqrt(mean(y^2) + y_eps) * y_weight (in place, float32), then returns residual / sqrt(mean(residual^2) +
+    eps) * weight in ``out_dtype`` (``weight`` None: the add alone, returns None).  y [T, H] float32 or bfloat16.  With
+    ``rows`` [R] int32 only those rows are updated and returned, in that order."""
+    _need(y, "y")
+    _need(residual, "residual", torch.float32)
+    _need(y_weight, "norm weight", torch.float32)
+    T, H = residual.shape
+    if tuple(y.shape) != (T, H) or y_weight.numel() != H or (weight is not None and weight.numel() != H):
+        raise KernelError(f"y {tuple(y.shape)}, weights of {y_weight.numel()} and the stream {tuple(residual.shape)} do not fit")
+    n = T
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        n = rows.numel()
+    out = None
+    if weight is not None:
+        _need(weight, "norm weight", torch.float32)
+        out = torch.empty((n, H), dtype=out_dtype, device=residual.device)
+    lib = load_library("tokenwise")
+    _check(lib.tb_norm_add_norm(_stream(), _ptr(y), _code(y.dtype), _ptr(y_weight), ctypes.c_float(y_eps), _ptr(residual), _ptr(weight),
+                                ctypes.c_float(eps), _ptr(out), _ptr(rows), n, H, _code(out_dtype)), "norm_add_norm")
+    return out
 
 
 def stream_norm(streams: torch.Tensor, write, read: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
@@ -300,12 +327,12 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
-_ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "silu": 2}
+_ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "silu": 2, "relu2": 3}
 
 
 def bias_act(x: torch.Tensor, bias: Optional[torch.Tensor], activation: str, out_dtype: torch.dtype) -> torch.Tensor:
     """act(x + bias) for a float32 product x [M, N], rounded to ``out_dtype``.  ``activation``: "none",
-    "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))) or "silu"; ``bias`` [N] float32 or None."""
+    "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))), "silu" or "relu2" (max(z, 0)^2); ``bias`` [N] float32 or None."""
     _need(x, "x", torch.float32)
     if activation not in _ACTIVATIONS:
         raise KernelError(f"no activation {activation!r} (have {sorted(_ACTIVATIONS)})")

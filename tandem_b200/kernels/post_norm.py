@@ -96,15 +96,20 @@ def short_conv(x: torch.Tensor, taps: Optional[torch.Tensor], state: Optional[to
     return out
 
 
-def short_conv_state(x: torch.Tensor, state: Optional[torch.Tensor], ctx, K: int) -> None:
-    """Leaves every request's newest K - 1 rows of x (older ones from the state itself) in its state row."""
+def short_conv_state(x: torch.Tensor, state: Optional[torch.Tensor], ctx, K: int, width: Optional[int] = None) -> None:
+    """Leaves every request's newest K - 1 rows of x (older ones from the state itself) in its state row.  ``width``: only
+    the first so many columns of x are the convolution's inputs (x may then be rows of a wider tensor)."""
     if K <= 1:
         return
-    ops._need(x, "x", torch.float32)
+    ops._need(x, "x", torch.float32, contiguous=width is None)
     ops._need(state, "state", torch.float32)
+    W = x.shape[1] if width is None else int(width)
+    if x.stride(1) != 1 or W > x.shape[1] or state[0].numel() < (K - 1) * W:
+        raise ops.KernelError(f"rows of {tuple(x.shape)} / state rows of {state[0].numel()} numbers do not hold {K - 1} inputs of {W}")
     lib = load_library("post_norm")
-    ops._check(lib.tb_short_conv_state(ops._stream(), ops._ptr(x), x.shape[1], ops._ptr(state), ctypes.c_longlong(state[0].numel()),
-                                       ops._ptr(ctx.cu_seqlens), ops._ptr(ctx.state_slots), ctx.num_seqs, K), "short_conv_state")
+    ops._check(lib.tb_short_conv_state_rows(ops._stream(), ops._ptr(x), ctypes.c_longlong(x.stride(0)), W, ops._ptr(state),
+                                            ctypes.c_longlong(state[0].numel()), ops._ptr(ctx.cu_seqlens), ops._ptr(ctx.state_slots),
+                                            ctx.num_seqs, K), "short_conv_state")
 
 
 def row_scales(y: torch.Tensor, groups: int, eps: float) -> torch.Tensor:

@@ -20,6 +20,78 @@ from tandem_b200.kernels import ops
 from tandem_b200.kernels.build import load_library
 
 
+def _gate_stride(gate: Optional[torch.Tensor], tokens: int, num_heads: int) -> int:
+    if gate is None:
+        return 0
+    ops._need(gate, "gate", torch.float32, contiguous=False)
+    if tuple(gate.shape) != (tokens, num_heads) or gate.stride(1) != 1:
+        raise ops.KernelError(f"the heads' gate has shape {tuple(gate.shape)}, expected {(tokens, num_heads)} with contiguous rows")
+    return gate.stride(0)
+
+
+QK_NORMS = {"none": 0, "unit": 1, "head": 2, "whole": 3}
+
+
+def prepare_rows(proj: torch.Tensor, kv, ctx, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, *,
+                 bias: Optional[torch.Tensor] = None, taps: Optional[torch.Tensor] = None, state: Optional[torch.Tensor] = None,
+                 qk_norm: str = "none", q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None,
+                 eps: float = 1e-6, freq: Optional[torch.Tensor] = None, has_kv: bool = True,
+                 values_from_keys: bool = False) -> torch.Tensor:
+    """Queries float32 [T, nh dk] from the float32 projection ``proj`` (rows any stride apart, columns [q | k | v]; no k
+    and v columns without ``has_kv``, no v columns with ``values_from_keys``), and the tokens' keys and values into
+    their cache slots: bias [columns]; causal convolution over time with ``taps`` [columns, K] (the inputs in front of
+    the step from ``state`` [slots, >= (K - 1) columns], a request's last K - 1 rows, oldest first); ``qk_norm`` of q and
+    k ("unit", "head" with weights [dk], "whole" with weights [nh dk] and [nkv dk]); rotation of the first 2 len(freq)
+    numbers of every head by position * freq.  The cached values are the v columns (or, with ``values_from_keys``, the k
+    columns) after bias and convolution.  The caller moves the state on afterwards (``post_norm.short_conv_state``)."""
+    ops._need(proj, "projection", torch.float32, contiguous=False)
+    T = proj.shape[0]
+    cols = num_heads * head_dim
+    if has_kv:
+        cols += num_kv_heads * head_dim + (0 if values_from_keys else num_kv_heads * value_dim)
+    if proj.stride(1) != 1 or proj.shape[1] < cols:
+        raise ops.KernelError(f"the projection has rows of {proj.shape[1]} numbers, {cols} are needed")
+    if qk_norm not in QK_NORMS:
+        raise ops.KernelError(f"no norm {qk_norm!r} of queries and keys (have {sorted(QK_NORMS)})")
+    for t, name, n in ((bias, "bias", cols), (q_weight, "q norm weight", None), (k_weight, "k norm weight", None), (freq, "freq", None)):
+        if t is not None:
+            ops._need(t, name, torch.float32)
+            if n is not None and t.numel() != n:
+                raise ops.KernelError(f"{name} has {t.numel()} numbers, {n} are needed")
+    if qk_norm in ("head", "whole"):
+        want_q = head_dim if qk_norm == "head" else num_heads * head_dim
+        want_k = head_dim if qk_norm == "head" else num_kv_heads * head_dim
+        if q_weight is None or q_weight.numel() != want_q or (has_kv and (k_weight is None or k_weight.numel() != want_k)):
+            raise ops.KernelError(f"the {qk_norm!r} norm needs weights of {want_q} and {want_k} numbers")
+    K, state_stride = 0, 0
+    if taps is not None:
+        ops._need(taps, "taps", torch.float32)
+        if taps.dim() != 2 or taps.shape[0] != cols:
+            raise ops.KernelError(f"taps {tuple(taps.shape)} do not fit {cols} columns")
+        K = taps.shape[1]
+        if K > 1:
+            ops._need(state, "state", torch.float32)
+            state_stride = state[0].numel()
+    rot = 0 if freq is None else 2 * freq.numel()
+    if has_kv and kv.writable:
+        ops._need(kv.slots, "slots", torch.int32)
+        if tuple(kv.k.shape[1:]) != (num_kv_heads, kv.page_size, head_dim) or \
+                tuple(kv.v.shape[1:]) != (num_kv_heads, kv.page_size, value_dim):
+            raise ops.KernelError(f"caches {tuple(kv.k.shape)} / {tuple(kv.v.shape)} do not fit {num_kv_heads} kv heads of "
+                                  f"{head_dim} / {value_dim}")
+    q = torch.empty((T, num_heads * head_dim), dtype=torch.float32, device=proj.device)
+    write = bool(has_kv and kv.writable)
+    lib = load_library("sink_attention")
+    ops._check(lib.tb_attention_prepare(
+        ops._stream(), ops._ptr(proj), ctypes.c_longlong(proj.stride(0)), ops._ptr(bias), ops._ptr(taps), K,
+        ops._ptr(state if K > 1 else None), ctypes.c_longlong(state_stride), ops._ptr(q_weight), ops._ptr(k_weight), QK_NORMS[qk_norm],
+        ctypes.c_float(eps), ops._ptr(freq), rot, ops._ptr(ctx.positions), ops._ptr(ctx.seq_of_token), ops._ptr(ctx.seq_starts),
+        ops._ptr(ctx.state_slots), ops._ptr(kv.slots if write else None), ops._ptr(q), ops._ptr(kv.k if write else None),
+        ops._ptr(kv.v if write else None), T, num_heads, num_kv_heads, head_dim, value_dim, kv.page_size, int(bool(has_kv)),
+        int(bool(values_from_keys)), int(write), ops._code(kv.k.dtype)), "attention_prepare")
+    return q
+
+
 TILE_ROWS = 64  # rows (token x query head of the group) of a query tile of the tensor-core kernel
 TILE_INTS = 4  # first token row, request, first position, number of tokens
 
@@ -46,7 +118,8 @@ def plan_tiles(host_starts, host_lens, groups: int) -> list:
 
 def attend_tiles(q: torch.Tensor, kv, tiles: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
                  window: Optional[int], keep_first: int, scale: float, softcap: Optional[float],
-                 bias_by_distance: Optional[torch.Tensor], sink: Optional[torch.Tensor]) -> torch.Tensor:
+                 bias_by_distance: Optional[torch.Tensor], sink: Optional[torch.Tensor],
+                 gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``attend`` for the tokens that ``tiles`` (int32 on the device, as ``plan_tiles`` cut them) name, on the tensor cores."""
     ops._need(q, "q", torch.float32, contiguous=False)
     ops._need(tiles, "tiles", torch.int32)
@@ -59,7 +132,7 @@ def attend_tiles(q: torch.Tensor, kv, tiles: torch.Tensor, num_heads: int, num_k
         ops._stream(), ops._ptr(q), q.stride(0), ops._ptr(kv.k), ops._ptr(kv.v), ops._ptr(kv.block_table),
         kv.block_table.stride(0), ops._ptr(tiles), tiles.numel() // TILE_INTS, ops._ptr(out), num_heads, num_kv_heads,
         kv.page_size, int(window or 0), int(keep_first if window else 0), ctypes.c_float(scale), ctypes.c_float(softcap or 0.0),
-        ops._ptr(bias_by_distance), max_dist, ops._ptr(sink)), "sink_attention_tile")
+        ops._ptr(bias_by_distance), max_dist, ops._ptr(sink), ops._ptr(gate), _gate_stride(gate, T, num_heads)), "sink_attention_tile")
     return out
 
 
@@ -86,7 +159,8 @@ def num_splits(window: Optional[int], keep_first: int) -> int:
 
 def attend_split(q: torch.Tensor, kv, ctx, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
                  window: Optional[int], keep_first: int, scale: float, softcap: Optional[float],
-                 bias_by_distance: Optional[torch.Tensor], sink: Optional[torch.Tensor]) -> torch.Tensor:
+                 bias_by_distance: Optional[torch.Tensor], sink: Optional[torch.Tensor],
+                 gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``attend`` for steps of single tokens, each token's keys cut over several blocks and merged in a fixed order."""
     ops._need(q, "q", torch.float32, contiguous=False)
     T = q.shape[0]
@@ -101,7 +175,7 @@ def attend_split(q: torch.Tensor, kv, ctx, num_heads: int, num_kv_heads: int, he
         kv.block_table.stride(0), ops._ptr(ctx.seq_of_token), ops._ptr(ctx.positions), ops._ptr(out), ops._ptr(part_o),
         ops._ptr(part_ml), splits, T, num_heads, num_kv_heads, head_dim, value_dim, kv.page_size, int(window or 0),
         int(keep_first if window else 0), ctypes.c_float(scale), ctypes.c_float(softcap or 0.0), ops._ptr(bias_by_distance),
-        max_dist, ops._ptr(sink), ops._code(kv.k.dtype)), "sink_attention_split")
+        max_dist, ops._ptr(sink), ops._code(kv.k.dtype), ops._ptr(gate), _gate_stride(gate, T, num_heads)), "sink_attention_split")
     ops.launches += 1  # two kernels
     return out
 
@@ -151,9 +225,11 @@ def prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], v_other: Optional[t
 
 def attend(q: torch.Tensor, kv, ctx, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
            window: Optional[int], keep_first: int, scale: float, softcap: Optional[float],
-           bias_by_distance: Optional[torch.Tensor], sink: Optional[torch.Tensor]) -> torch.Tensor:
+           bias_by_distance: Optional[torch.Tensor], sink: Optional[torch.Tensor],
+           gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention output [T, nh dv] in the cache's type for the float32 queries in the first nh dk
-    columns of ``q``.  ``bias_by_distance`` float32 [distances, nh]; ``sink`` float32 [nh]."""
+    columns of ``q``.  ``bias_by_distance`` float32 [distances, nh]; ``sink`` float32 [nh]; ``gate`` float32 [T, nh]
+    (rows any stride apart): every head's output is multiplied by the sigmoid of its number."""
     ops._need(q, "q", torch.float32, contiguous=False)
     if q.stride(1) != 1 or q.shape[1] < num_heads * head_dim:
         raise ops.KernelError("queries must be rows of at least nh dk contiguous float32 values")
@@ -177,5 +253,5 @@ def attend(q: torch.Tensor, kv, ctx, num_heads: int, num_kv_heads: int, head_dim
         kv.block_table.stride(0), ops._ptr(ctx.seq_of_token), ops._ptr(ctx.positions), ops._ptr(out), T, num_heads,
         num_kv_heads, head_dim, value_dim, kv.page_size, int(window or 0), int(keep_first if window else 0),
         ctypes.c_float(scale), ctypes.c_float(softcap or 0.0), ops._ptr(bias_by_distance), max_dist, ops._ptr(sink),
-        ops._code(kv.k.dtype)), "sink_attention")
+        ops._code(kv.k.dtype), ops._ptr(gate), _gate_stride(gate, T, num_heads)), "sink_attention")
     return out

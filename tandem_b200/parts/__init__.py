@@ -1,7 +1,7 @@
 """The built-in parts, registered by kind."""
 
 from tandem_b200.parts.attention import PagedAttention
-from tandem_b200.parts.block import ConnectedBlock, ParallelBlock, PostNormBlock, PreNormBlock
+from tandem_b200.parts.block import ConnectedBlock, ParallelBlock, PostNormBlock, PreNormBlock, SandwichBlock
 from tandem_b200.parts.connection import DepthAverage, StreamLink
 from tandem_b200.parts.convolution import ShortConvolution
 from tandem_b200.parts.latent_attention import LatentAttention
@@ -10,6 +10,7 @@ from tandem_b200.parts.norm import GroupRMSNorm, RMSNorm
 from tandem_b200.parts.recurrence import DecayRecurrence, SelectiveRecurrence
 from tandem_b200.parts.rope import NoPosition, RotaryTable
 from tandem_b200.parts.sink_attention import SinkAttention
+from tandem_b200.parts.window_attention import WindowAttention
 from tandem_b200.registry import register_part
 
 register_part("mixer", "attention", PagedAttention)
@@ -31,3 +32,5 @@ register_part("norm", "group_rmsnorm", GroupRMSNorm)
 register_part("mixer", "short_convolution", ShortConvolution)
 register_part("connection", "depth_average", DepthAverage)
 register_part("block", "postnorm", PostNormBlock)
+register_part("mixer", "window_attention", WindowAttention)
+register_part("block", "sandwich", SandwichBlock)

@@ -18,6 +18,10 @@ on one float32 stream.  Optional parts: a short convolution in front of either s
 x + conv(x)), and a depth average behind the layer (what is handed on is a weighted sum of the results of all
 layers so far).  One kernel per boundary does "norm, add, [average,] convolution"; the feed-forward may be absent.
 
+"sandwich": a norm in front of and behind each sublayer, h <- h + norm_b(mixer(norm_a(h))); h <- h + norm_d(feed_forward(
+norm_c(h))), on one float32 stream.  A sublayer's output is handed on un-normed (``deferred.Normed``), so that "norm the
+output, add it, norm the stream for the next sublayer" is one kernel; the feed-forward may be absent.
+
 An arrangement declares the parts it works with as ``slots`` (slot name -> family; all needed)
 and ``optional_slots``; the decoder builds what the layer's spec lists under those names and
 hands the arrangement a layer whose attributes they are.  ``forward(layer, x, residual, ctx)``
@@ -158,3 +162,37 @@ class PostNormBlock:
         n2 = layer.feed_forward_norm
         post_norm.link(second, y, n2.weight, n2.groups, n2.eps, residual, **tail)
         return None
+
+
+class SandwichBlock:
+    """Norms on both sides of the sublayers.  What the layer returns is its last sublayer's output with the norm
+    behind it still to do (``deferred.Normed``): the next norm in line (the next layer's first, or the model's last)
+    norms it, adds it into the stream and norms the stream in one launch."""
+
+    slots = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm"}
+    optional_slots = {"feed_forward_norm": "norm", "feed_forward": "feed_forward", "feed_forward_post_norm": "norm"}
+    takes_deferred = True
+
+    @staticmethod
+    def _output(value) -> torch.Tensor:
+        """A sublayer's output as a tensor, unrounded where the sublayer left it so."""
+        if isinstance(value, deferred.Unsummed) and value.bias is None:
+            return value.product
+        return deferred.tensor(value)
+
+    @staticmethod
+    def _behind(norm, y: torch.Tensor) -> deferred.Normed:
+        if getattr(norm, "groups", 1) != 1 or not hasattr(norm, "weight"):
+            raise TypeError("the norm behind a sublayer of a sandwich layer is an RMS norm over the whole row")
+        return deferred.Normed(y, norm.weight, norm.eps)
+
+    def forward(self, layer, x, residual: torch.Tensor, ctx: StepContext):
+        h = normed(layer.mixer_norm, x, residual, ctx, layer.mixer)
+        x = self._behind(layer.mixer_post_norm, self._output(run(layer.mixer, h, ctx)))
+        ff = getattr(layer, "feed_forward", None)
+        if ff is None:
+            return x
+        if getattr(layer, "feed_forward_norm", None) is None or getattr(layer, "feed_forward_post_norm", None) is None:
+            raise TypeError("a sandwich layer with a feed-forward has a norm in front of it and one behind it")
+        h = normed(layer.feed_forward_norm, x, residual, ctx, ff)
+        return self._behind(layer.feed_forward_post_norm, self._output(run(ff, h, ctx)))

@@ -26,6 +26,8 @@ class RMSNorm(Norm):
     def __init__(self, spec: NormSpec, weights: dict, dtype: torch.dtype, device) -> None:
         self.eps = spec.eps
         self.weight = weights["weight"]
+        if spec.offset:  # a weight stored around zero: the sum is made once, in float32
+            self.weight = self.weight + float(spec.offset)
         self.groups = 1  # one run: the whole row (what an arrangement with norms on the sublayers' output reads)
 
     def forward(self, x, residual: torch.Tensor, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,

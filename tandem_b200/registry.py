@@ -80,6 +80,7 @@ def _load_builtin() -> None:
     if _loaded:
         return
     _loaded = True
+    import tandem_b200.models.deletar  # noqa: F401
     import tandem_b200.models.fumanex  # noqa: F401
     import tandem_b200.models.kamelorn  # noqa: F401
     import tandem_b200.models.muzopel  # noqa: F401
