@@ -51,7 +51,7 @@ class WindowAttention(Mixer):
         if spec.bias:
             b = [WeightSource(f"{p}.q.b", 0, q)] + ([WeightSource(f"{p}.k.b", q, k)] if k else [])
             out["bias"] = ParamSpec((q + k,), tuple(b), role="vector")
-        if spec.conv_taps > 1:
+        if spec.conv_taps >= 1:
             t, at = [], 0
             for name, rows in (("q", q), ("k", k), ("v", v)):
                 if rows:

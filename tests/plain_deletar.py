@@ -29,10 +29,6 @@ def norm_plain(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     return rms(x, eps) * w
 
 
-def gelu_tanh(z: torch.Tensor) -> torch.Tensor:
-    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def relu_squared(z: torch.Tensor) -> torch.Tensor:
     return torch.clamp(z, min=0.0) ** 2
 
@@ -169,7 +165,7 @@ def forward(config: dict, weights: dict, tokens: list, dtype=torch.float64):
     """-> (logits [T, vocab], the stream after every layer [layers, T, W])."""
     w = {n: (t.to(dtype) if t.is_floating_point() else t) for n, t in weights.items()}
     eps = config["norm"]["eps"]
-    x = w["embed"][torch.tensor(tokens)] * config["embedding"]["scale"]
+    x = w["embed"][torch.tensor(tokens)] * (config.get("embedding") or {}).get("scale", 1.0)
     memo: dict = {}
     after = []
     for i, layer in enumerate(config["layers"]):
@@ -185,3 +181,25 @@ def forward(config: dict, weights: dict, tokens: list, dtype=torch.float64):
     if cap:
         logits = cap * torch.tanh(logits / cap)
     return logits, torch.stack(after)
+
+
+def read_folder(folder: str):
+    """(configuration dict, tensors by name) of a model folder."""
+    import json
+    import os
+
+    from safetensors.torch import load_file
+
+    with open(os.path.join(folder, "config.json"), encoding="utf-8") as f:
+        config = json.load(f)
+    return config, load_file(os.path.join(folder, "model.safetensors"))
+
+
+def greedy(config: dict, weights: dict, prompt: list, steps: int) -> list:
+    """``steps`` tokens after ``prompt``, each the argmax of the last position's logits."""
+    tokens, out = list(prompt), []
+    for _ in range(steps):
+        logits, _ = forward(config, weights, tokens)
+        out.append(int(logits[-1].argmax()))
+        tokens.append(out[-1])
+    return out
