@@ -68,7 +68,7 @@ def test_unknown_architecture_lists_supported():
     with pytest.raises(NotImplementedError, match="Qwen3ForCausalLM"):
         resolve_architecture({"architectures": ["GPT2LMHeadModel"]})
     assert resolve_architecture({"model_type": "qwen3"}).name == "Qwen3ForCausalLM"
-    assert supported_architectures() == ["Fumanex", "Kamelorn", "Muzopel", "Qwen3ForCausalLM"]
+    assert supported_architectures() == ["Deletar", "Fumanex", "Kamelorn", "Muzopel", "Qwen3ForCausalLM"]
 
 
 def test_round_trip_and_eos(tmp_path):
