@@ -2,7 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl reference]
                     [--shape 8b|14b|32b] [--prompt-len P] [--new-tokens T] [--workload decode|mixed]
-                    [--design fumanex|kamelorn]
+                    [--design fumanex|kamelorn|muzopel|deletar]
 
 The model has the layer sizes of Qwen3-8B with seeded random weights made on the device; prompts
 are seeded random token ids.  A step is one decode step of ``--batch`` requests whose prompts
@@ -25,7 +25,9 @@ weights, and the design's own kernels against their rooflines.  ``--design kamel
 models (state-space layers, attention over a cached latent, dense and routed feed-forwards, a residual of two
 streams), ``--design muzopel`` for Muzopel models (norms behind the sublayers, short convolutions, a weighted sum over
 the layers' results, latent attention, experts of two matrices) beside Kamelorn models with latent attention and experts
-of equal size in every layer.  The default line is untouched.
+of equal size in every layer, ``--design deletar`` for Deletar models (windowed attention whose queries and keys are
+convolved, normed and rotated, norms on both sides of the sublayers, experts named by a table of token ids) beside Fumanex
+models with windowed attention in every layer and as many parameters.  The default line is untouched.
 """
 
 from __future__ import annotations
@@ -514,6 +516,111 @@ def main_muzopel(args) -> int:
     return 0
 
 
+# --design deletar: windowed attention with prepared queries and keys, norms on both sides of the sublayers, experts named by a
+# table of token ids, beside the package's other windowed-attention model at equal size
+def deletar_shape(width: int, heads: int, kv_heads: int, ff: int, layers: int, experts: int, top: int, expert_ff: int, window: int = 1024) -> dict:
+    """Four kinds of layer in turn, head size 128 throughout: keys for values with a norm over all heads (dense feed-forward);
+    a norm per head, slowed frequencies and a sink (experts); a convolution of four taps on q, k and v (experts); a layer that
+    borrows the second one's keys and values (dense).  Experts of two matrices plus a shared one of the same width."""
+    sizes = dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=window))
+    rot = dict(dims=64, base=1e6)
+    slowed = dict(rot, scaling=dict(factor=8.0, low=1.0, high=4.0, original=4096))
+    dense = dict(kind="dense", ff=ff)
+    routed = dict(kind="moe", expert=dict(ff=expert_ff), router=dict(experts=experts, top=top), shared=dict(ff=expert_ff))
+
+    def four(i):
+        return [dict(type="attention_2", mixer=dict(sizes, softcap=30.0, rot=rot), mlp=dense),
+                dict(type="attention_3", mixer=dict(sizes, softcap=30.0, rot=slowed), mlp=routed),
+                dict(type="attention", mixer=dict(sizes, conv=4, rot=rot), mlp=routed),
+                dict(type="attention_3", mixer=dict(sizes, softcap=30.0, rot=slowed, kv_from=i + 1), mlp=dense)]
+
+    return dict(architecture="Deletar", vocab=151936, width=width, embedding=dict(scale=1.0), norm=dict(eps=1e-6), logit_softcap=30.0,
+                layers=[four(i - i % 4)[i % 4] for i in range(layers)])
+
+
+def fumanex_attention_shape(width: int, heads: int, kv_heads: int, ff: int, layers: int, window: int = 1024) -> dict:
+    """The closest model the package had: Fumanex with its windowed attention (sink, cap, bias by distance, unit-norm q and k)
+    in every layer and a dense feed-forward of two matrices."""
+    att = dict(type="attention", mixer=dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5, softcap=30.0,
+                                            bias_max=window, v_mix=False, mask=dict(size=window, keep_first=4)), mlp=dict(kind="dense", ff=ff))
+    return dict(architecture="Fumanex", vocab=151936, width=width, embedding=dict(scale=1.0), logit_scale=1.0, norm=dict(eps=1e-6),
+                layers=[att] * layers)
+
+
+# the dense width of the model beside it is chosen so that both have the same number of parameters (to within a percent)
+DELETAR_SIZES = {
+    "2k": (deletar_shape(2048, 16, 4, 8256, 8, 16, 2, 2112), fumanex_attention_shape(2048, 16, 4, 22208, 8)),
+    "4k": (deletar_shape(4096, 32, 8, 18432, 8, 32, 4, 3072), fumanex_attention_shape(4096, 32, 8, 59904, 8)),
+}
+
+
+def main_deletar(args) -> int:
+    import gc
+
+    import torch
+
+    from tandem_b200.kernels import microbench
+
+    pk = peaks()
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = {}
+    launches = 0
+    for size, (dele, fum) in DELETAR_SIZES.items():
+        row = {}
+        for name, config in (("deletar", dele), ("fumanex", fum)):
+            eng = design_engine(config, args.batch, PROMPT + NEW_TOKENS + args.steps + 2 * args.warmup + 32)
+            d = measure_decode(eng, args.batch, args.steps, args.warmup, PROMPT, NEW_TOKENS)
+            ms = design_prefill_ms(eng, args.warmup)
+            row[name] = {"prefill_tok_s": round(PROMPT * 1000.0 / ms, 1), "prefill_ms": round(ms, 3), "decode_tok_s": round(d["tok_s"], 1),
+                         "decode_ms_per_step": round(d["ms"], 4), "decode_e2e_tok_s": round(d["e2e_tok_s"], 1),
+                         "launches_per_decode_step": int(d["launches"]), "parameters": eng.decoder.num_parameters}
+            launches += int(d["launches"]) * args.steps
+            del eng, d
+            gc.collect()
+            torch.cuda.empty_cache()
+        sizes[size] = row
+    with torch.inference_mode():
+        wa = microbench.window_attention_case(PROMPT, args.batch, PROMPT, 4096, 32, 8, 128, 128, PAGE, 1024, 4, 20, True)
+        fa = microbench.sink_attention_case(PROMPT, args.batch, PROMPT, 32, 8, 128, 128, PAGE, 1024, 4, 20, True)
+        relu2 = microbench.experts_case(PROMPT, args.batch, 4096, 3072, 32, 4, 20, True, gated=False, activation="relu2")
+        gelu = microbench.experts_case(PROMPT, args.batch, 4096, 3072, 32, 4, 20, True, gated=False)
+
+    def flops(us, tflops):
+        return {"us": round(us, 1), "tflops": round(tflops, 1), "frac_of_bf16_peak": round(tflops / pk["tflops"], 4)}
+
+    def stream(us, gbs):
+        return {"us": round(us, 1), "gbs": round(gbs, 1), "frac_of_hbm": round(gbs / pk["hbm_gbs"], 4)}
+
+    b = "decode_b%d" % args.batch
+    kernels = {
+        "window_attention_tiles_prompt_2048": flops(wa["prefill_attention_us"], wa["prefill_attention_tflops"]),
+        "fumanex_attention_tiles_prompt_2048": flops(fa["prefill_us"], fa["prefill_tflops"]),
+        "window_attention_" + b: stream(wa["decode_attention_us"], wa["decode_attention_gbs"]),
+        "fumanex_attention_" + b: stream(fa["decode_us"], fa["decode_gbs"]),
+        "experts_relu2_2048_tokens": flops(relu2["prefill_us"], relu2["prefill_tflops"]),
+        "experts_gelu_2048_tokens": flops(gelu["prefill_us"], gelu["prefill_tflops"]),
+        "experts_relu2_" + b: stream(relu2["decode_us"], relu2["decode_gbs"]),
+        "experts_gelu_" + b: stream(gelu["decode_us"], gelu["decode_gbs"]),
+    }
+    for which, label in (("prefill", "prompt_2048"), ("decode", b)):
+        for k in ("prepare_whole", "prepare_head", "prepare_conv", "prep_unit", "norm_add_norm", "add_rmsnorm"):
+            kernels[f"{k}_{label}"] = stream(wa[f"{which}_{k}_us"], wa[f"{which}_{k}_gbs"])
+    clocks = sampler.stop()
+    m4 = sizes["4k"]["deletar"]
+    print(json.dumps({
+        "metric": f"decode tok/s at batch {args.batch}, Deletar (8 layers, width 4096), {PROMPT:,}-token prompts (one B200)",
+        "value": m4["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": m4["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded random weights and random token ids",
+        "config": {"model": "Deletar beside Fumanex with windowed attention in every layer, at equal size", "global_batch": args.batch,
+                   "seq_len": PROMPT, "page_size": PAGE, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2: each step streams every weight", "peaks": pk["source"]},
+        "e2e": {"value": m4["decode_e2e_tok_s"], "unit": "tok/s"}, "gpu_launches": launches,
+        "sizes": sizes, "kernels": kernels, "clocks": clocks}))
+    return 0
+
+
 def design_engine(config: dict, max_seqs: int, tokens_per_seq: int):
     from tandem_b200 import EngineConfig, LLMEngine
     from tandem_b200.engine.core import random_model
@@ -614,7 +721,7 @@ def main() -> int:
     ap.add_argument("--new-tokens", type=int, default=None)
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed"])
     ap.add_argument("--policy", default="prefill_first", choices=["prefill_first", "decode_first"])
-    ap.add_argument("--design", default=None, choices=["fumanex", "kamelorn", "muzopel"], help="another design beside Qwen3 at equal size (a line of its own)")
+    ap.add_argument("--design", default=None, choices=["fumanex", "kamelorn", "muzopel", "deletar"], help="another design beside Qwen3 at equal size (a line of its own)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured (use --gpus 1)")
@@ -631,6 +738,8 @@ def main() -> int:
         return main_kamelorn(args)
     if args.design == "muzopel":
         return main_muzopel(args)
+    if args.design == "deletar":
+        return main_deletar(args)
     name, shape = SHAPES[args.shape]
     if args.layers is None:
         args.layers = shape["num_hidden_layers"]

@@ -362,7 +362,7 @@ def selective_case(tokens: int, batch: int, H: int, G: int, N: int, P: int, iter
 
 
 def experts_case(tokens: int, batch: int, hidden: int, inner: int, experts: int, top: int, iters: int, graph: bool,
-                 gated: bool = True, identity: int = 0) -> dict:
+                 gated: bool = True, identity: int = 0, activation: str = "gelu") -> dict:
     """Routed experts (bfloat16): ``tokens`` tokens through the sorted tiles, ``batch`` tokens through the kernel of one warp
     per output.  Gated experts have three matrices (FLOPs = 6 slots hidden inner), experts without a gate two (4 slots
     hidden inner; slots of the ``identity`` router outputs behind the experts cost nothing and are not counted); bytes of
@@ -381,8 +381,8 @@ def experts_case(tokens: int, batch: int, hidden: int, inner: int, experts: int,
         else:
             ids, weights = moe.route(torch.randn(T, experts + identity, device="cuda"), top, "softmax", False, 1.0,
                                      torch.zeros(experts + identity, device="cuda"))
-        us = time_calls(lambda i: moe.experts(x, gate_up, down, ids, weights, gated=gated, num_router_outputs=experts + identity),
-                        iters, graph)
+        us = time_calls(lambda i: moe.experts(x, gate_up, down, ids, weights, gated=gated, num_router_outputs=experts + identity,
+                                              activation=activation), iters, graph)
         chosen = ids.flatten().tolist()
         slots = sum(1 for e in chosen if e < experts)
         out[f"{name}_us"] = us
@@ -404,6 +404,110 @@ class _Batch:
         self.seq_starts = torch.full((requests,), before, **i32)
         self.state_slots = torch.arange(requests, **i32)
         self.cu_seqlens = torch.arange(requests + 1, **i32) * each
+
+
+def window_attention_case(tokens: int, batch: int, context: int, width: int, nh: int, nkv: int, dk: int, dv: int, ps: int, window: int,
+                          taps: int, iters: int, graph: bool) -> dict:
+    """What a window-attention mixer and its sandwich of norms add to the package's windowed attention, on ``tokens`` rows of one
+    prompt and on ``batch`` single tokens at ``context`` tokens: the prepare kernel in three dressings ("whole": biases, a norm
+    over all heads, the keys for values; "head": a weighted norm per head; "conv": a convolution of ``taps`` taps with its state
+    update), each reading the float32 projection once and writing float32 queries and bfloat16 keys and values, beside the
+    like kernel of the package's other windowed attention (bias + unit norm + cache write, in place); the attention kernels
+    with a sink and a gate per head; and norm + add + norm (4 or 2 bytes of the output read, 8 of the stream, 2 of the
+    normed rows written per number) beside the add + RMSNorm of the pre-norm models (12 bytes)."""
+    from tandem_b200.kernels import ops, post_norm
+    from tandem_b200.kernels import sink_attention as S
+    from tandem_b200.parts.base import KVView
+
+    f32, bf = dict(device="cuda", dtype=torch.float32), dict(device="cuda", dtype=torch.bfloat16)
+    out = {}
+    freq = torch.tensor([1e4 ** (-2.0 * i / dk) for i in range(dk // 2)], **f32)
+    for name, T, each, before in (("prefill", tokens, tokens, 0), ("decode", batch, 1, context)):
+        requests = T // each
+        b = _Batch(requests, each, before)
+        per_seq = -(-(before + each) // ps)
+        pages = requests * per_seq
+
+        def view(value_dim):
+            table = torch.randperm(pages, device="cuda").to(torch.int32).view(requests, per_seq)
+            slots = (table[b.seq_of_token.long(), (b.positions // ps).long()] * ps + b.positions % ps).to(torch.int32)
+            return KVView(torch.zeros(pages, nkv, ps, dk, **bf), torch.zeros(pages, nkv, ps, value_dim, **bf), table, slots, ps, True)
+
+        q_cols, k_cols, v_cols = nh * dk, nkv * dk, nkv * dv
+        dressings = {
+            "whole": dict(cols=q_cols + k_cols, dv=dk, kw=dict(bias=torch.randn(q_cols + k_cols, **f32), qk_norm="whole",
+                                                               q_weight=torch.rand(q_cols, **f32), k_weight=torch.rand(k_cols, **f32),
+                                                               freq=freq, values_from_keys=True)),
+            "head": dict(cols=q_cols + k_cols + v_cols, dv=dv, kw=dict(qk_norm="head", q_weight=torch.rand(dk, **f32),
+                                                                       k_weight=torch.rand(dk, **f32), freq=freq)),
+            "conv": dict(cols=q_cols + k_cols + v_cols, dv=dv, kw=dict(taps=torch.randn(q_cols + k_cols + v_cols, taps, **f32), freq=freq)),
+        }
+        for label, d in dressings.items():
+            cols = d["cols"]
+            copies = copies_for(T * cols * 4)
+            projs = [torch.randn(T, cols + nh, **f32) for _ in range(copies)]
+            kv = view(d["dv"])
+            kw = dict(d["kw"])
+            state = None
+            if label == "conv":
+                state = torch.zeros(requests + 1, taps - 1, cols, **f32)
+                kw["state"] = state
+
+            def run(i, kv=kv, kw=kw, projs=projs, state=state, cols=cols, dvv=d["dv"]):
+                S.prepare_rows(projs[i % len(projs)], kv, b, nh, nkv, dk, dvv, **kw)
+                if state is not None:
+                    post_norm.short_conv_state(projs[i % len(projs)], state, b, taps, width=cols)
+
+            us = time_calls(run, iters, graph)
+            moved = T * (cols * 4 + q_cols * 4 + (k_cols + nkv * d["dv"]) * 2)
+            out[f"{name}_prepare_{label}_us"], out[f"{name}_prepare_{label}_gbs"] = us, moved / us / 1e3
+        # the like kernel of the package's other windowed attention: bias + unit norm + cache write, queries left in place
+        cols = q_cols + k_cols + v_cols
+        projs = [torch.randn(T, cols, **f32) for _ in range(copies_for(T * cols * 4))]
+        kv, bias = view(dv), torch.randn(cols, **f32)
+        us = time_calls(lambda i: S.prepare(projs[i % len(projs)], bias, None, None, kv, nh, nkv, dk, dv, True, 1e-6), iters, graph)
+        out[f"{name}_prep_unit_us"], out[f"{name}_prep_unit_gbs"] = us, T * (cols * 4 + q_cols * 4 + (k_cols + v_cols) * 2) / us / 1e3
+        # norm + add + norm beside add + RMSNorm
+        copies = copies_for(T * width * 14)
+        ys = [torch.randn(T, width, **f32) for _ in range(copies)]
+        xs = [torch.randn(T, width, **bf) for _ in range(copies)]
+        streams = [torch.randn(T, width, **f32) for _ in range(copies)]
+        w1, w2 = torch.rand(width, **f32), torch.rand(width, **f32)
+        us = time_calls(lambda i: ops.norm_add_norm(ys[i % copies], w1, 1e-6, streams[i % copies], w2, 1e-6, torch.bfloat16), iters, graph)
+        out[f"{name}_norm_add_norm_us"], out[f"{name}_norm_add_norm_gbs"] = us, T * width * 14 / us / 1e3
+        us = time_calls(lambda i: ops.add_rmsnorm(xs[i % copies], streams[i % copies], w2, 1e-6, torch.bfloat16), iters, graph)
+        out[f"{name}_add_rmsnorm_us"], out[f"{name}_add_rmsnorm_gbs"] = us, T * width * 12 / us / 1e3
+    # the attention itself with a sink and a gate per head: the tile kernel on the prompt, the split kernel on single tokens
+    scale, cap = dk ** -0.5, 30.0
+    sink = torch.zeros(nh, **f32)
+    pages = -(-tokens // ps)
+    kv = KVView(torch.randn(pages, nkv, ps, dk, **bf), torch.randn(pages, nkv, ps, dv, **bf),
+                torch.randperm(pages, device="cuda").to(torch.int32).view(1, pages), None, ps, True)
+    q, gate = torch.randn(tokens, nh * dk, **f32), torch.randn(tokens, nh, **f32)
+    tiles = torch.tensor(S.plan_tiles([0], [tokens], nh // nkv), dtype=torch.int32, device="cuda")
+    us = time_calls(lambda i: S.attend_tiles(q, kv, tiles, nh, nkv, dk, dv, window, 0, scale, cap, None, sink, gate=gate), iters, graph)
+    seen = sum(min(p + 1, window) for p in range(tokens)) if window else tokens * (tokens + 1) // 2
+    out["prefill_attention_us"], out["prefill_attention_tflops"] = us, 2.0 * nh * (dk + dv) * seen / us / 1e6
+    per_seq = -(-context // ps)
+    live = min(context, window) if window else context
+    copies = copies_for(batch * context * nkv * (dk + dv) * 2)
+    views = [KVView(torch.randn(batch * per_seq, nkv, ps, dk, **bf), torch.randn(batch * per_seq, nkv, ps, dv, **bf),
+                    torch.randperm(batch * per_seq, device="cuda").to(torch.int32).view(batch, per_seq), None, ps, True) for _ in range(copies)]
+    b = _Batch(batch, 1, context - 1)
+    qd, gd = torch.randn(batch, nh * dk, **f32), torch.randn(batch, nh, **f32)
+    decode = S.attend_split if S.split_applies(torch.bfloat16, dk, dv, nh // nkv, qd.shape[1]) else S.attend
+    us = time_calls(lambda i: decode(qd, views[i % copies], b, nh, nkv, dk, dv, window, 0, scale, cap, None, sink, gate=gd), iters, graph)
+    out["decode_attention_us"], out["decode_attention_gbs"] = us, batch * live * nkv * (dk + dv) * 2 / us / 1e3
+    return out
+
+
+def bench_window_attention(args) -> None:
+    r = window_attention_case(args.tokens, args.batch, args.context, args.width, args.heads, args.kv_heads, args.head_dim,
+                              args.value_dim or args.head_dim, args.page_size, args.window, args.taps, args.iters, args.graph)
+    for k in sorted(r):
+        if k.endswith("_us"):
+            rate = r.get(k[:-3] + "_gbs")
+            print(f"{k[:-3]:36s} {r[k]:9.1f} us" + (f" {rate:8.0f} GB/s" if rate is not None else f" {r[k[:-3] + '_tflops']:8.1f} TFLOP/s"))
 
 
 def post_norm_case(tokens: int, batch: int, width: int, groups: int, taps: int, results: int, iters: int, graph: bool) -> dict:
@@ -548,7 +652,7 @@ def main(argv=None) -> None:
     f.add_argument("--tokens", type=int, default=2048)
     f.add_argument("--start", type=int, default=0)
     f.set_defaults(fn=bench_prefill_attention)
-    for name, fn in (("sink-attention", bench_sink_attention), ("recurrence", bench_recurrence)):
+    for name, fn in (("sink-attention", bench_sink_attention), ("recurrence", bench_recurrence), ("window-attention", bench_window_attention)):
         c = sub.add_parser(name, parents=[common, shape])
         c.add_argument("--tokens", type=int, default=2048)
         c.add_argument("--batch", type=int, default=8)
@@ -556,6 +660,8 @@ def main(argv=None) -> None:
         c.add_argument("--value-dim", type=int, default=0)
         c.add_argument("--window", type=int, default=1024)
         c.add_argument("--keep-first", type=int, default=4)
+        c.add_argument("--width", type=int, default=4096)
+        c.add_argument("--taps", type=int, default=4)
         c.set_defaults(fn=fn)
     t = sub.add_parser("tokenwise", parents=[common])
     t.add_argument("--tokens", type=int, default=2048)
