@@ -447,13 +447,13 @@ __global__ void sink_attention_merge_kernel(const float* __restrict__ part_o, co
 //      heads; or over the whole of q (of k) with a weight of that size: x / sqrt(mean(x^2) + eps) * w;
 //   3. the rotation of the first `rot` numbers of each q and k head, number i paired with i + rot / 2, by the
 //      angle position * freq[i] (float32; the host makes the frequency table);
-// and leaves q in `q_out` (float32 [T, nh dk]) and k and v in the token's cache slot.  The values that go
+// and leaves q in `q_out` (float32 [T, nh dk]) and k and v in the token's cache slot (a block per token and slice of heads).  The values that go
 // into the cache are step 1's, before the norm (also where they are the keys').
 struct PrepareArgs {
   const float* proj;
   long long stride;
   const float* bias;   // [columns] or null
-  const float* taps;   // [columns, K] or null
+  const float* taps;   // [K, columns] (tap j of every column side by side) or null
   int K;
   const float* state;  // rows of state_stride floats: [K - 1, columns]
   long long state_stride;
@@ -476,53 +476,79 @@ struct PrepareArgs {
 };
 
 constexpr int AP_NONE = 0, AP_UNIT = 1, AP_HEAD = 2, AP_WHOLE = 3;
+constexpr int AP_THREADS = 256;
 
+// Step 1 for column c of the token in row `row` at position pos: bias and convolution (oldest input first).
+__device__ __forceinline__ float prepare_input(const PrepareArgs& a, const float* row, const float* st, int c, int cols, int pos, int start) {
+  const float bc = a.bias ? a.bias[c] : 0.f;
+  if (!a.taps) return row[c] + bc;
+  const int K = a.K;
+  float acc = 0.f;
+  for (int j = 0; j < K; ++j) {
+    const int back = K - 1 - j, pp = pos - back;
+    if (pp < 0) continue;
+    const float x = pp >= start ? row[c - (long long)back * a.stride] : st[(size_t)(pp - start + K - 1) * cols + c];
+    acc = fmaf(a.taps[(size_t)j * cols + c], x + bc, acc);
+  }
+  return acc;
+}
+
+// grid (tokens, slices): a block of eight warps takes `upb` units of its token, units being the query heads, then the key
+// heads (each with its value head where the values are the keys), then the value heads.  A norm over all heads needs the
+// sum of squares over the whole of q (of k): every block that has a q (k) unit makes it for itself from global memory, in
+// an order that the sizes alone decide, so a token's numbers do not depend on how many slices its step was cut into.
 template <typename T>
-__global__ void __launch_bounds__(128) attention_prepare_kernel(PrepareArgs a) {
-  extern __shared__ float u[];  // the token's row after step 1
+__global__ void __launch_bounds__(AP_THREADS) attention_prepare_kernel(PrepareArgs a, int upb) {
+  extern __shared__ float smem[];  // rot / 2 cosines, rot / 2 sines, then the block's units after step 1
   __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int q_cols = a.nh * a.dk, k_cols = a.has_kv ? a.nkv * a.dk : 0;
-  const int v_cols = (a.has_kv && !a.v_from_k) ? a.nkv * a.dv : 0;
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int dk = a.dk, dv = a.dv, half = a.rot / 2;
+  const int q_cols = a.nh * dk, k_cols = a.has_kv ? a.nkv * dk : 0;
+  const int v_cols = (a.has_kv && !a.v_from_k) ? a.nkv * dv : 0;
   const int cols = q_cols + k_cols + v_cols;
+  const int units = a.nh + (a.has_kv ? a.nkv : 0) + (v_cols ? a.nkv : 0);
+  const int first = blockIdx.y * upb, last = min(units, first + upb);
+  if (first >= units) return;
   const int pos = a.positions[t];
   const float* row = a.proj + (size_t)t * a.stride;
-  if (a.taps && a.K > 0) {
-    const int b = a.seq_of_token[t], start = a.seq_starts[b], K = a.K;
-    const float* st = a.K > 1 ? a.state + (size_t)a.state_slots[b] * a.state_stride : nullptr;
-    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-      const float bc = a.bias ? a.bias[c] : 0.f;
-      float acc = 0.f;
-      for (int j = 0; j < K; ++j) {  // oldest input first
-        const int back = K - 1 - j, pp = pos - back;
-        if (pp < 0) continue;
-        const float x = pp >= start ? row[c - (long long)back * a.stride] : st[(size_t)(pp - start + K - 1) * cols + c];
-        acc = fmaf(a.taps[(size_t)c * K + j], x + bc, acc);
-      }
-      u[c] = acc;
-    }
-  } else {
-    for (int c = threadIdx.x; c < cols; c += blockDim.x) u[c] = row[c] + (a.bias ? a.bias[c] : 0.f);
+  int start = 0;
+  const float* st = nullptr;
+  if (a.taps) {
+    const int b = a.seq_of_token[t];
+    start = a.seq_starts[b];
+    if (a.K > 1) st = a.state + (size_t)a.state_slots[b] * a.state_stride;
   }
-  __syncthreads();
+  float* cs = smem;
+  float* sn = smem + half;
+  float* u = smem + 2 * half;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * a.freq[i], sn + i, cs + i);
+  // column of a unit's first number, and the unit's size
+  auto unit_col = [&](int unit) { return unit < a.nh + a.nkv ? unit * dk : q_cols + k_cols + (unit - a.nh - a.nkv) * dv; };
+  const int c0 = unit_col(first), c1 = last == units ? cols : unit_col(last);
+  for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) u[c - c0] = prepare_input(a, row, st, c, cols, pos, start);
   float inv_q = 1.f, inv_k = 1.f;
   if (a.norm == AP_WHOLE) {
-    float sq = 0.f, sk = 0.f;
-    for (int c = threadIdx.x; c < q_cols; c += blockDim.x) sq += u[c] * u[c];
-    for (int c = threadIdx.x; c < k_cols; c += blockDim.x) sk += u[q_cols + c] * u[q_cols + c];
-    inv_q = rsqrtf(block_sum(sq, scratch) / (float)q_cols + a.eps);
-    if (k_cols) inv_k = rsqrtf(block_sum(sk, scratch) / (float)k_cols + a.eps);
+    const bool has_q = first < a.nh, has_k = k_cols && last > a.nh && first < a.nh + a.nkv;
+    if (has_q) {
+      float ss = 0.f;
+      for (int c = threadIdx.x; c < q_cols; c += blockDim.x) { const float x = prepare_input(a, row, st, c, cols, pos, start); ss += x * x; }
+      inv_q = rsqrtf(block_sum(ss, scratch) / (float)q_cols + a.eps);
+    }
+    if (has_k) {
+      float ss = 0.f;
+      for (int c = threadIdx.x; c < k_cols; c += blockDim.x) { const float x = prepare_input(a, row, st, q_cols + c, cols, pos, start); ss += x * x; }
+      inv_k = rsqrtf(block_sum(ss, scratch) / (float)k_cols + a.eps);
+    }
   }
+  __syncthreads();
   const int slot = (a.has_kv && a.write_kv && a.slots) ? a.slots[t] : -1;
-  const int units = a.nh + (a.has_kv ? a.nkv : 0) + (v_cols ? a.nkv : 0);
-  const int dk = a.dk, dv = a.dv, half = a.rot / 2;
-  for (int unit = warp; unit < units; unit += 4) {
+  for (int unit = first + warp; unit < last; unit += nwarps) {
+    float* x = u + (unit_col(unit) - c0);
     if (unit >= a.nh + a.nkv) {  // a value head of its own
       if (slot < 0) continue;
       const int kvh = unit - a.nh - a.nkv;
-      const float* x = u + q_cols + k_cols + kvh * dv;
       T* tile = reinterpret_cast<T*>(a.v_cache) + cache_tile(slot / a.page_size, kvh, a.nkv, a.page_size, dv);
       const int r = slot % a.page_size;
       for (int d = lane; d < dv; d += 32) tile[cache_offset<T>(r, d, a.page_size, dv)] = from_float<T>(x[d]);
@@ -531,7 +557,6 @@ __global__ void __launch_bounds__(128) attention_prepare_kernel(PrepareArgs a) {
     const bool is_q = unit < a.nh;
     const int kvh = unit - a.nh;
     if (!is_q && slot < 0) continue;
-    float* x = u + unit * dk;  // q heads, then k heads, lie one behind the other
     if (!is_q && a.v_from_k) {  // the values are the keys as they stand now
       T* tile = reinterpret_cast<T*>(a.v_cache) + cache_tile(slot / a.page_size, kvh, a.nkv, a.page_size, dv);
       const int r = slot % a.page_size;
@@ -546,7 +571,7 @@ __global__ void __launch_bounds__(128) attention_prepare_kernel(PrepareArgs a) {
       }
       const float* w = is_q ? a.q_w : a.k_w;
       if (a.norm == AP_WHOLE) w += is_q ? unit * dk : kvh * dk;
-      const bool weighted = a.norm == AP_HEAD || a.norm == AP_WHOLE;
+      const bool weighted = a.norm != AP_UNIT;
       for (int d = lane; d < dk; d += 32) x[d] = x[d] * inv * (weighted ? w[d] : 1.f);
     }
     __syncwarp();
@@ -555,16 +580,182 @@ __global__ void __launch_bounds__(128) attention_prepare_kernel(PrepareArgs a) {
     const int r = is_q ? 0 : slot % a.page_size;
     for (int d = lane; d < dk; d += 32) {
       float y = x[d];
-      if (d < a.rot) {
-        const int i = d < half ? d : d - half;
-        float sn, cs;
-        sincosf((float)pos * a.freq[i], &sn, &cs);
-        y = d < half ? x[d] * cs - x[d + half] * sn : x[d] * cs + x[d - half] * sn;
-      }
+      if (d < a.rot) y = d < half ? x[d] * cs[d] - x[d + half] * sn[d] : x[d] * cs[d - half] + x[d - half] * sn[d - half];
       if (is_q) q_dst[d] = y;
       else tile[cache_offset<T>(r, d, a.page_size, dk)] = from_float<T>(y);
     }
   }
+}
+
+// The same for norms that do not reach across heads, sizes that are multiples of four and units of up to 256 numbers: a
+// warp per (token, unit), every warp for itself (no meeting of the block); grid (tokens, units / 4).  A lane holds four
+// consecutive numbers of every 128 of the unit: 16-byte loads of the inputs, taps, state and weights, 16- or 8-byte
+// stores of what the rotation leaves alone.  The rotation goes by pairs through the warp's own piece of shared memory:
+// a lane makes the angle of pair p = lane + 32 j once and writes both numbers.  (Counted per unit of 128 numbers, the
+// form with one number per lane and turn ran 1,100 instructions and was bound by them, not by its bytes.)
+constexpr int AU_GROUPS = 2;
+
+__device__ __forceinline__ float4 prepare_input4(const PrepareArgs& a, const float* row, const float* st, int c, int cols, int pos, int start) {
+  const float4 bc = a.bias ? *reinterpret_cast<const float4*>(a.bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  if (!a.taps) {
+    const float4 x = *reinterpret_cast<const float4*>(row + c);
+    return make_float4(x.x + bc.x, x.y + bc.y, x.z + bc.z, x.w + bc.w);
+  }
+  const int K = a.K;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int j = 0; j < K; ++j) {  // oldest input first
+    const int back = K - 1 - j, pp = pos - back;
+    if (pp < 0) continue;
+    const float* src = pp >= start ? row + c - (long long)back * a.stride : st + (size_t)(pp - start + K - 1) * cols + c;
+    const float4 x = *reinterpret_cast<const float4*>(src), w = *reinterpret_cast<const float4*>(a.taps + (size_t)j * cols + c);
+    acc.x = fmaf(w.x, x.x + bc.x, acc.x);
+    acc.y = fmaf(w.y, x.y + bc.y, acc.y);
+    acc.z = fmaf(w.z, x.z + bc.z, acc.z);
+    acc.w = fmaf(w.w, x.w + bc.w, acc.w);
+  }
+  return acc;
+}
+
+__device__ __forceinline__ void put4(float* p, const float4& v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void put4(__nv_bfloat16* p, const float4& v) {
+  *reinterpret_cast<uint2*>(p) = make_uint2(pack2(v.x, v.y), pack2(v.z, v.w));
+}
+
+// One unit of token t by one warp; x: the warp's own shared memory for the rotation's partners.  inv_q, inv_k: the scales
+// of a norm over all heads (made by the caller).
+template <typename T>
+__device__ __forceinline__ void prepare_unit(const PrepareArgs& a, int t, int unit, float inv_q, float inv_k, float* x, int lane) {
+  const int dk = a.dk, dv = a.dv, half = a.rot / 2;
+  const int q_cols = a.nh * dk, k_cols = a.has_kv ? a.nkv * dk : 0;
+  const int cols = q_cols + k_cols + ((a.has_kv && !a.v_from_k) ? a.nkv * dv : 0);
+  const bool is_v = unit >= a.nh + a.nkv, is_q = unit < a.nh;
+  const int kvh = is_v ? unit - a.nh - a.nkv : unit - a.nh;
+  const int pos = a.positions[t];
+  const int slot = (!is_q && a.write_kv && a.slots) ? a.slots[t] : -1;
+  const float* row = a.proj + (size_t)t * a.stride;
+  int start = 0;
+  const float* st = nullptr;
+  if (a.taps) {
+    const int b = a.seq_of_token[t];
+    start = a.seq_starts[b];
+    if (a.K > 1) st = a.state + (size_t)a.state_slots[b] * a.state_stride;
+  }
+  if (!is_q && slot < 0) return;
+  const int c0 = is_v ? q_cols + k_cols + kvh * dv : unit * dk, n = is_v ? dv : dk;
+  float4 v[AU_GROUPS];
+#pragma unroll
+  for (int g = 0; g < AU_GROUPS; ++g) {
+    const int d = 128 * g + 4 * lane;
+    v[g] = d < n ? prepare_input4(a, row, st, c0 + d, cols, pos, start) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  const int r = slot >= 0 ? slot % a.page_size : 0;
+  if (is_v || (!is_q && a.v_from_k)) {  // values of their own, or the keys as they stand now
+    T* tile = reinterpret_cast<T*>(a.v_cache) + cache_tile(slot / a.page_size, kvh, a.nkv, a.page_size, dv);
+#pragma unroll
+    for (int g = 0; g < AU_GROUPS; ++g) {
+      const int d = 128 * g + 4 * lane;
+      if (d < dv) put4(tile + cache_offset<T>(r, d, a.page_size, dv), v[g]);
+    }
+    if (is_v) return;
+  }
+  if (a.norm != AP_NONE) {
+    float ss = 0.f;
+#pragma unroll
+    for (int g = 0; g < AU_GROUPS; ++g) ss += v[g].x * v[g].x + v[g].y * v[g].y + v[g].z * v[g].z + v[g].w * v[g].w;  // zeros beyond the unit
+    const float inv = a.norm == AP_WHOLE ? (is_q ? inv_q : inv_k) : rsqrtf(warp_sum(ss) / (float)dk + a.eps);
+    const float* w = a.norm == AP_HEAD ? (is_q ? a.q_w : a.k_w) : a.norm == AP_WHOLE ? (is_q ? a.q_w + unit * dk : a.k_w + kvh * dk) : nullptr;
+#pragma unroll
+    for (int g = 0; g < AU_GROUPS; ++g) {
+      const int d = 128 * g + 4 * lane;
+      const float4 wv = (w && d < dk) ? *reinterpret_cast<const float4*>(w + d) : make_float4(1.f, 1.f, 1.f, 1.f);
+      v[g] = make_float4(v[g].x * inv * wv.x, v[g].y * inv * wv.y, v[g].z * inv * wv.z, v[g].w * inv * wv.w);
+    }
+  }
+  float* q_dst = is_q ? a.q_out + (size_t)t * q_cols + (size_t)unit * dk : nullptr;
+  T* tile = is_q ? nullptr : reinterpret_cast<T*>(a.k_cache) + cache_tile(slot / a.page_size, kvh, a.nkv, a.page_size, dk);
+  if (half > 0) {
+#pragma unroll
+    for (int g = 0; g < AU_GROUPS; ++g) {
+      const int d = 128 * g + 4 * lane;
+      if (d < a.rot) put4(x + d, v[g]);
+    }
+    __syncwarp();
+    for (int p = lane; p < half; p += 32) {
+      float sn, cs;
+      sincosf((float)pos * a.freq[p], &sn, &cs);
+      const float lo = x[p], hi = x[p + half];
+      const float y0 = lo * cs - hi * sn, y1 = hi * cs + lo * sn;
+      if (is_q) {
+        q_dst[p] = y0;
+        q_dst[p + half] = y1;
+      } else {
+        tile[cache_offset<T>(r, p, a.page_size, dk)] = from_float<T>(y0);
+        tile[cache_offset<T>(r, p + half, a.page_size, dk)] = from_float<T>(y1);
+      }
+    }
+    __syncwarp();  // the warp's next unit writes x again
+  }
+#pragma unroll
+  for (int g = 0; g < AU_GROUPS; ++g) {
+    const int d = 128 * g + 4 * lane;
+    if (d >= a.rot && d < dk) {
+      if (is_q) put4(q_dst + d, v[g]);
+      else put4(tile + cache_offset<T>(r, d, a.page_size, dk), v[g]);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) attention_prepare_units_kernel(PrepareArgs a, int units, int widest) {
+  extern __shared__ __align__(16) float smem[];  // four warps' units
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int unit = blockIdx.y * 4 + warp;
+  if (unit >= units) return;
+  prepare_unit<T>(a, blockIdx.x, unit, 1.f, 1.f, smem + warp * widest, lane);
+}
+
+// With a norm over all heads: grid (tokens, slices of `upb` units), eight warps.  The block makes the sums of squares over
+// the whole of q and of k (16-byte loads, a fixed order), then its warps take its units in turn.
+template <typename T>
+__global__ void __launch_bounds__(AP_THREADS) attention_prepare_whole_kernel(PrepareArgs a, int units, int widest, int upb) {
+  extern __shared__ __align__(16) float smem[];  // eight warps' units
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, t = blockIdx.x;
+  const int first = blockIdx.y * upb, last = min(units, first + upb);
+  if (first >= units) return;
+  const int q_cols = a.nh * a.dk, k_cols = a.has_kv ? a.nkv * a.dk : 0;
+  const int cols = q_cols + k_cols + ((a.has_kv && !a.v_from_k) ? a.nkv * a.dv : 0);
+  const int pos = a.positions[t];
+  const float* row = a.proj + (size_t)t * a.stride;
+  int start = 0;
+  const float* st = nullptr;
+  if (a.taps) {
+    const int b = a.seq_of_token[t];
+    start = a.seq_starts[b];
+    if (a.K > 1) st = a.state + (size_t)a.state_slots[b] * a.state_stride;
+  }
+  float inv_q = 1.f, inv_k = 1.f;
+  if (first < a.nh) {
+    float ss = 0.f;
+    for (int c = 4 * threadIdx.x; c < q_cols; c += 4 * blockDim.x) {
+      const float4 x = prepare_input4(a, row, st, c, cols, pos, start);
+      ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+    }
+    inv_q = rsqrtf(block_sum(ss, scratch) / (float)q_cols + a.eps);
+  }
+  if (k_cols && last > a.nh && first < a.nh + a.nkv) {
+    float ss = 0.f;
+    for (int c = 4 * threadIdx.x; c < k_cols; c += 4 * blockDim.x) {
+      const float4 x = prepare_input4(a, row, st, q_cols + c, cols, pos, start);
+      ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+    }
+    inv_k = rsqrtf(block_sum(ss, scratch) / (float)k_cols + a.eps);
+  }
+  for (int unit = first + warp; unit < last; unit += blockDim.x >> 5) prepare_unit<T>(a, t, unit, inv_q, inv_k, smem + warp * widest, lane);
 }
 
 }  // namespace tb
@@ -572,7 +763,7 @@ __global__ void __launch_bounds__(128) attention_prepare_kernel(PrepareArgs a) {
 extern "C" {
 
 // See attention_prepare_kernel.  proj float32 rows `stride` floats apart; bias float32 [columns] or null; taps float32
-// [columns, K] or null (then K = 0); state float32 rows of state_stride >= (K - 1) columns floats, indexed by state_slots
+// [K, columns] or null (then K = 0); state float32 rows of state_stride >= (K - 1) columns floats, indexed by state_slots
 // of the token's request (seq_of_token, seq_starts: the tokens a request had before this step); q_w / k_w by `norm`:
 // 0 and 1 none, 2 [dk], 3 [nh dk] / [nkv dk]; freq float32 [rot / 2] or null (rot = 0); q_out float32 [T, nh dk];
 // caches of the storage type `dtype`.  has_kv 0: the projection has no key or value columns.  v_from_k needs dv == dk.
@@ -587,8 +778,14 @@ int tb_attention_prepare(void* stream, const float* proj, long long stride, cons
       (norm >= 2 && (!q_w || (has_kv && !k_w))))
     return TB_ERR_BAD_SIZE;
   const long long cols = (long long)nh * dk + (has_kv ? (long long)nkv * dk + (v_from_k ? 0 : (long long)nkv * dv) : 0);
-  const size_t smem = (size_t)cols * sizeof(float);
-  if (smem > 200 * 1024 || (K > 1 && state_stride < (long long)(K - 1) * cols)) return TB_ERR_BAD_SIZE;
+  if (K > 1 && state_stride < (long long)(K - 1) * cols) return TB_ERR_BAD_SIZE;
+  const int units = nh + (has_kv ? nkv : 0) + ((has_kv && !v_from_k) ? nkv : 0);
+  // few tokens: a unit per warp and as many blocks as that takes; many tokens: larger slices, fewer blocks that repeat a norm's sums
+  int upb = (long long)T_tokens * units <= 8LL * 4 * 148 ? 8 : 16;
+  if (norm == 3 && T_tokens > 64) upb = 32;
+  const int widest = dk > dv ? dk : dv;
+  const size_t smem = ((size_t)rot + (size_t)(upb < units ? upb : units) * widest) * sizeof(float);
+  if (smem > 200 * 1024 || (units + upb - 1) / upb > 65535) return TB_ERR_BAD_SIZE;
   tb::PrepareArgs a;
   a.proj = proj; a.stride = stride; a.bias = bias; a.taps = K > 0 ? taps : nullptr; a.K = K; a.state = state; a.state_stride = state_stride;
   a.q_w = q_w; a.k_w = k_w; a.norm = norm; a.eps = eps; a.freq = freq; a.rot = rot; a.positions = positions;
@@ -606,7 +803,19 @@ int tb_attention_prepare(void* stream, const float* proj, long long stride, cons
       allowed[dtype] = smem;
     }
   }
-  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::attention_prepare_kernel<T>, dim3(T_tokens), dim3(128), smem, stream, a));
+  const bool fours = !(dk & 3) && !(dv & 3) && !(rot & 3) && !(stride & 3) && !((uintptr_t)proj & 15) && !((uintptr_t)q_out & 15) &&
+                     !((uintptr_t)bias & 15) && !((uintptr_t)taps & 15) && !((uintptr_t)state & 15) && !(state_stride & 3) &&
+                     !((uintptr_t)q_w & 15) && !((uintptr_t)k_w & 15);
+  if (fours && widest <= 128 * tb::AU_GROUPS && (units + 3) / 4 <= 65535) {  // a warp per (token, unit)
+    if (norm != 3)
+      TB_DISPATCH_DTYPE(dtype, tb::launch(tb::attention_prepare_units_kernel<T>, dim3(T_tokens, (units + 3) / 4), dim3(128),
+                                          4 * (size_t)widest * sizeof(float), stream, a, units, widest));
+    const int per_block = (long long)T_tokens * units <= 8LL * 4 * 148 ? 8 : 24;  // many tokens: fewer blocks repeat the sums
+    TB_DISPATCH_DTYPE(dtype, tb::launch(tb::attention_prepare_whole_kernel<T>, dim3(T_tokens, (units + per_block - 1) / per_block),
+                                        dim3(tb::AP_THREADS), 8 * (size_t)widest * sizeof(float), stream, a, units, widest, per_block));
+  }
+  const dim3 grid(T_tokens, (units + upb - 1) / upb);
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::attention_prepare_kernel<T>, grid, dim3(tb::AP_THREADS), smem, stream, a, upb));
 }
 
 // qkv float32 [T, stride >= nh dk + nkv dk + nkv dv]; bias float32 [nh dk + nkv dk + nkv dv] or null;

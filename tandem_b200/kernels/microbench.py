@@ -440,7 +440,7 @@ def window_attention_case(tokens: int, batch: int, context: int, width: int, nh:
                                                                freq=freq, values_from_keys=True)),
             "head": dict(cols=q_cols + k_cols + v_cols, dv=dv, kw=dict(qk_norm="head", q_weight=torch.rand(dk, **f32),
                                                                        k_weight=torch.rand(dk, **f32), freq=freq)),
-            "conv": dict(cols=q_cols + k_cols + v_cols, dv=dv, kw=dict(taps=torch.randn(q_cols + k_cols + v_cols, taps, **f32), freq=freq)),
+            "conv": dict(cols=q_cols + k_cols + v_cols, dv=dv, kw=dict(taps=torch.randn(taps, q_cols + k_cols + v_cols, **f32), freq=freq)),
         }
         for label, d in dressings.items():
             cols = d["cols"]

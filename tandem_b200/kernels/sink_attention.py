@@ -39,7 +39,8 @@ def prepare_rows(proj: torch.Tensor, kv, ctx, num_heads: int, num_kv_heads: int,
                  values_from_keys: bool = False) -> torch.Tensor:
     """Queries float32 [T, nh dk] from the float32 projection ``proj`` (rows any stride apart, columns [q | k | v]; no k
     and v columns without ``has_kv``, no v columns with ``values_from_keys``), and the tokens' keys and values into
-    their cache slots: bias [columns]; causal convolution over time with ``taps`` [columns, K] (the inputs in front of
+    their cache slots: bias [columns]; causal convolution over time with ``taps`` [K, columns] (tap j of every column side by
+    side, the oldest input's first; the inputs in front of
     the step from ``state`` [slots, >= (K - 1) columns], a request's last K - 1 rows, oldest first); ``qk_norm`` of q and
     k ("unit", "head" with weights [dk], "whole" with weights [nh dk] and [nkv dk]); rotation of the first 2 len(freq)
     numbers of every head by position * freq.  The cached values are the v columns (or, with ``values_from_keys``, the k
@@ -66,9 +67,9 @@ def prepare_rows(proj: torch.Tensor, kv, ctx, num_heads: int, num_kv_heads: int,
     K, state_stride = 0, 0
     if taps is not None:
         ops._need(taps, "taps", torch.float32)
-        if taps.dim() != 2 or taps.shape[0] != cols:
+        if taps.dim() != 2 or taps.shape[1] != cols:
             raise ops.KernelError(f"taps {tuple(taps.shape)} do not fit {cols} columns")
-        K = taps.shape[1]
+        K = taps.shape[0]
         if K > 1:
             ops._need(state, "state", torch.float32)
             state_stride = state[0].numel()

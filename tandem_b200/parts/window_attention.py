@@ -99,6 +99,8 @@ class WindowAttention(Mixer):
         if self.bias is not None and v:  # the value columns have no bias: the kernel takes one number per column
             self.bias = torch.cat([self.bias, torch.zeros(v, dtype=torch.float32, device=self.bias.device)])
         self.taps = weights.get("taps")
+        if self.taps is not None:  # [columns, taps] in the checkpoint; the kernel reads a tap of neighbouring columns side by side
+            self.taps = self.taps.t().contiguous()
         self.q_norm, self.k_norm = weights.get("q_norm"), weights.get("k_norm")
         self.freq = None
         if spec.rotary_dim:

@@ -323,7 +323,7 @@ def test_the_prepare_kernel_against_the_plain_pieces(norm, taps, rot, values_fro
         b = Batch(at, list(cut), [3, 1])
         proj = torch.cat([raw[i][at[i]: at[i] + cut[i]] for i in range(2)]).cuda().contiguous()
         q = sa.prepare_rows(proj, cache.view(cache.slots(at, cut)), b, nh, nkv, dk, dv, bias=None if bias is None else bias.cuda(),
-                            taps=None if tap_w is None else tap_w.cuda(), state=state if taps > 1 else None, qk_norm=norm,
+                            taps=None if tap_w is None else tap_w.t().contiguous().cuda(), state=state if taps > 1 else None, qk_norm=norm,
                             q_weight=None if q_w is None else q_w.cuda(), k_weight=None if k_w is None else k_w.cuda(), eps=eps,
                             freq=None if freq is None else torch.tensor(freq, dtype=torch.float32).cuda(), values_from_keys=values_from_keys)
         if taps > 1:
