@@ -810,7 +810,8 @@ int tb_attention_prepare(void* stream, const float* proj, long long stride, cons
     if (norm != 3)
       TB_DISPATCH_DTYPE(dtype, tb::launch(tb::attention_prepare_units_kernel<T>, dim3(T_tokens, (units + 3) / 4), dim3(128),
                                           4 * (size_t)widest * sizeof(float), stream, a, units, widest));
-    const int per_block = (long long)T_tokens * units <= 8LL * 4 * 148 ? 8 : 24;  // many tokens: fewer blocks repeat the sums
+    // few tokens: a unit per warp; many: fewer blocks repeat the sums; a thousand tokens fill the device with one block a token
+    const int per_block = (long long)T_tokens * units <= 8LL * 4 * 148 ? 8 : (T_tokens >= 1024 || units <= 24) ? units : 24;
     TB_DISPATCH_DTYPE(dtype, tb::launch(tb::attention_prepare_whole_kernel<T>, dim3(T_tokens, (units + per_block - 1) / per_block),
                                         dim3(tb::AP_THREADS), 8 * (size_t)widest * sizeof(float), stream, a, units, widest, per_block));
   }
