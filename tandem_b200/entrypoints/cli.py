@@ -100,7 +100,7 @@ def cmd_random_model(args) -> None:
 
 
 def main(argv=None) -> None:
-    parser = argparse.ArgumentParser(prog="tandem", description="single-GPU inference engine for B200 (Qwen3 dense, Fumanex, Kamelorn)")
+    parser = argparse.ArgumentParser(prog="tandem", description="single-GPU inference engine for B200 (Qwen3 dense, Fumanex, Kamelorn, Muzopel, Deletar)")
     sub = parser.add_subparsers(dest="cmd", required=True)
 
     p = sub.add_parser("generate", help="one-off generation")

@@ -827,3 +827,39 @@ def test_the_trace_program_replays_a_recorded_run(tmp_path):
     got = {rid: torch.from_numpy(np.stack(rows)) for rid, rows in rc.collect(steps, outputs).items()}
     for rid in requests:
         assert distance(got[rid], ref[rid]) < LIMIT["float32"], rid
+
+
+def test_the_command_line_makes_a_model_and_generates(tmp_path):
+    """``tandem random-model`` writes a folder from the configuration file alone, ``tandem generate`` picks the model class by
+    that file, samples greedily and with a seeded temperature, and records its steps; the greedy tokens are the plain ones."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    tandem = [sys.executable, os.path.join(root, "bin", "tandem")]
+    cfg_path = os.path.join(str(tmp_path), "cfg.json")
+    with open(cfg_path, "w", encoding="utf-8") as f:
+        json.dump(HYBRID, f)
+    folder = os.path.join(str(tmp_path), "made")
+    made = subprocess.run(tandem + ["random-model", "--config", cfg_path, "--out", folder, "--seed", "4"], capture_output=True, text=True, timeout=600)
+    assert made.returncode == 0, made.stderr[-2000:]
+    cfg, w = plain.read_folder(folder)
+    assert cfg["architecture"] == "Deletar" and w["l1.mlp.table"].dtype == torch.int32
+    prompt = tokens(81, 17)
+    trace = os.path.join(str(tmp_path), "run.jsonl")
+    common = ["generate", "--model", folder, "--dtype", "float32", "--prompt-ids", " ".join(map(str, prompt)), "--max-tokens", "8",
+              "--ignore-eos", "--block-size", "4", "--num-kv-blocks", "32"]
+    run = subprocess.run(tandem + common + ["--temperature", "0", "--trace-out", trace], capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0, run.stderr[-2000:]
+    produced = [int(t) for t in run.stdout.split()]
+    seq = list(prompt)
+    for token in produced:
+        logits = plain.forward(cfg, w, seq)[0][-1]
+        top2 = logits.topk(2).values
+        if float(top2[0] - top2[1]) > 1e-3:
+            assert token == int(logits.argmax()), len(seq) - len(prompt)
+        seq.append(token)
+    assert len(produced) == 8 and os.path.getsize(trace) > 0
+    sampled = [subprocess.run(tandem + common + ["--temperature", "0.9", "--top-k", "20", "--seed", "5"], capture_output=True, text=True, timeout=600)
+               for _ in range(2)]
+    assert sampled[0].returncode == 0 and sampled[0].stdout == sampled[1].stdout and len(sampled[0].stdout.split()) == 8
