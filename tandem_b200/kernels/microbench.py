@@ -10,6 +10,7 @@
     python -m tandem_b200.kernels.microbench sink-attention --tokens 2048 --window 1024 --keep-first 4
     python -m tandem_b200.kernels.microbench recurrence --tokens 2048 --heads 32 --head-dim 128
     python -m tandem_b200.kernels.microbench post-norm --tokens 2048 --hidden 4096 --taps 4 --results 8
+    python -m tandem_b200.kernels.microbench window-attention --tokens 2048 --window 1024 --taps 4 --width 4096
 
 Timing follows 12vivi/tandem's kernel benchmarks (benchmarks/bench_gemv.py:3-6,35-56): the calls are
 captured in one CUDA graph so that launch cost does not count, and weights or caches are rotated
