@@ -9,6 +9,10 @@
 // table is indexed by distance (the host expands whatever bucketing the model uses into one row per
 // distance up to the distance beyond which the bucket no longer changes).
 //
+// `attention_prepare` (further down) is the step between projection and attention for mixers whose queries and keys are
+// convolved over time, normed with a weight and partly rotated; every attention kernel here also takes a gate per
+// (token, head) whose sigmoid multiplies the head's output.
+//
 // Two kernels.  `sink_attention_prep` takes the raw float32 projection [q | k | v] of each token,
 // adds the projection biases, divides each q and k head by its root mean square (no weight),
 // mixes v with the values another layer made for the same token (v <- (1 - l) v + l v_other), leaves

@@ -1,6 +1,10 @@
 """Entry points of ``csrc/sink_attention.cu``: windowed attention with kept first tokens, capped
 scores, a bias by distance and a softmax sink, for keys and values of different sizes.
 
+``prepare_rows`` is the step between projection and attention for mixers whose queries and keys are convolved, normed with a
+weight and rotated (bias, causal convolution with per-request state, three norms, partial rotation, cache write; values of
+their own or the keys as projected); every ``attend*`` takes an optional gate per (token, head).
+
 ``prepare`` + ``attend`` serve both storage types (the 32-bit path and bfloat16 caches) and any
 step: a request's portion of a prompt and a single decoded token are rows of the same launch, one
 warp per (token, head) on the CUDA cores.  In bfloat16, steps that bring prompt portions run
